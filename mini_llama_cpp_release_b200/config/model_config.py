@@ -77,7 +77,7 @@ class ModelConfig:
             eos_token_id=_token_ids(raw.get("eos_token_id")),
         )
 
-    SHARED_KEYS = ("architectures", "vocab_size", "max_position_embeddings", "torch_dtype", "bos_token_id", "eos_token_id")
+    SHARED_KEYS = ("architectures", "architecture", "vocab_size", "max_position_embeddings", "torch_dtype", "bos_token_id", "eos_token_id")
 
     @classmethod
     def parse(cls, raw: Dict[str, Any]) -> "ModelConfig":
@@ -138,7 +138,13 @@ class ModelConfig:
 
 
 def architecture_of(raw: Dict[str, Any]) -> str:
+    """The model class a config.json names: the first entry of `architectures`, or, in files that name one class
+    only, the string `architecture`."""
     archs = raw.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
-        raise ConfigError("missing config key: architectures (a list whose first entry names the model class)")
-    return archs[0]
+    if archs and isinstance(archs, (list, tuple)) and isinstance(archs[0], str):
+        return archs[0]
+    one = raw.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError("missing config key: architectures (a list whose first entry names the model class), "
+                      "or architecture (its name)")

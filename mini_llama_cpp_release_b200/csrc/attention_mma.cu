@@ -44,6 +44,8 @@ struct MmaArgs {
     const int* start_pos;     // [B]
     float* part_ml;           // [N*H][n_splits][2]
     float* part_o;            // [N*H][n_splits][HD]
+    const float* sinks;       // [H] or null: exp(sinks[h]) joins head h's softmax denominator once, with no value; where the
+                              // key range is split, whoever merges the splits adds it
     float scale_log2;         // scale * log2(e)
     int q_heads;
     int group;
@@ -328,6 +330,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     }
 
     constexpr float LN2 = 0.6931471805599453f;
+    constexpr float LOG2E = 1.4426950408889634f;
     if (KP == 1) {
         // each warp owns its rows: write straight from registers
 #pragma unroll
@@ -337,7 +340,8 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
             const int t = r / GH, hg = chunk * GH + r % GH;
             const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
             if (a.n_splits == 1) {
-                const float inv = 1.0f / l[rr];
+                const float sink = a.sinks != nullptr ? exp2f(a.sinks[kvh * a.group + hg] * LOG2E - m[rr]) : 0.0f;
+                const float inv = 1.0f / (l[rr] + sink);
                 bf16* dst = a.out + row * HD + 2 * (lane & 3);
 #pragma unroll
                 for (int j = 0; j < NT_O; ++j)
@@ -399,6 +403,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
         }
         const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
         if (a.n_splits == 1) {
+            if (a.sinks != nullptr) L += exp2f(a.sinks[kvh * a.group + hg] * LOG2E - M);
             a.out[row * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
             const long long pr = row * a.n_splits + split;
@@ -831,6 +836,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
             }
         } else if (a.n_splits == 1) {
+            if (a.sinks != nullptr) L += exp2f(a.sinks[kvh * a.group + hg] * 1.4426950408889634f - PMLc[2 * r]);
             const float inv = 1.0f / L;
             *reinterpret_cast<uint2*>(a.out + row * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         } else {
@@ -869,6 +875,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
             }
             const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
+            if (a.sinks != nullptr) L += exp2f(a.sinks[kvh * a.group + hg] * 1.4426950408889634f - M);
             const float inv = 1.0f / L;
             *reinterpret_cast<uint2*>(a.out + row * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         }
@@ -1004,7 +1011,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
                                  int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
                                  int window, int row_tiles, int warp_private, int n_splits, float* part_ml, float* part_o,
                                  void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                 int pages_per_seq, int page_size, int pool_pages, int* status, void* stream) {
+                                 int pages_per_seq, int page_size, int pool_pages, int* status, const float* sinks, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd != HD || page_size != TILE) return MLC_ERR_BAD_SIZE;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
@@ -1022,6 +1029,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.start_pos = start_pos;
     a.part_ml = part_ml;
     a.part_o = part_o;
+    a.sinks = sinks;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.q_heads = q_heads;
     a.group = q_heads / kv_heads;

@@ -30,6 +30,7 @@ struct AttnArgs {
     const int* start_pos;     // [B] tokens cached before this step
     float* part_ml;           // [N*H][n_splits][2]   (n_splits > 1)
     float* part_o;            // [N*H][n_splits][hd]
+    const float* sinks;       // [H] or null: exp(sinks[h]) joins the softmax denominator of head h, once, with no value
     float scale;
     int q_heads;
     int group;                // query heads per kv head
@@ -166,7 +167,8 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
         const long long row = (long long)(seq_tok0 + tok0 + t) * a.q_heads + (kvh * a.group + hg);
         if (a.n_splits == 1) {
             T* o = (T*)a.out + row * hd;
-            const float inv = 1.0f / l[i];
+            const float sink = a.sinks != nullptr ? expf(a.sinks[kvh * a.group + hg] - m[i]) : 0.0f;
+            const float inv = 1.0f / (l[i] + sink);
 #pragma unroll
             for (int k = 0; k < ATT_ACC; ++k) {
                 const int d = lane + 32 * k;
@@ -192,7 +194,8 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
 // loads of a lane do not depend on each other, so they are in flight together.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_o,
-                                         long long n_rows, int n_splits, int hd, T* __restrict__ out) {
+                                         long long n_rows, int n_splits, int hd, const float* __restrict__ sinks, int q_heads,
+                                         T* __restrict__ out) {
     grid_launch_dependents();
     grid_dependency_wait();
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -208,6 +211,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_ml, cons
         if (ms != -INFINITY) L += __ldg(ml + 2 * s + 1) * expf(ms - M);
     }
     L = warp_sum(L);
+    if (sinks != nullptr) L += expf(sinks[row % q_heads] - M);      // rows are (token, head) pairs, heads fastest
     const float inv = 1.0f / L;
     const float* po = part_o + row * n_splits * hd;
     for (int d = lane; d < hd; d += 32) {
@@ -233,7 +237,7 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
                                  int n_seqs, int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
                                  int window, int n_splits, float* part_ml, float* part_o, void* k_pool, void* v_pool,
                                  const int* page_table, long long entry_offset, int pages_per_seq, int page_size,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, const float* sinks = nullptr) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd <= 0 || hd > ATT_MAX_HD || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return MLC_ERR_BAD_SIZE;
     if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
@@ -246,6 +250,7 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
     a.start_pos = start_pos;
     a.part_ml = part_ml;
     a.part_o = part_o;
+    a.sinks = sinks;
     a.scale = scale;
     a.q_heads = q_heads;
     a.group = q_heads / kv_heads;
@@ -284,9 +289,9 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
         const long long n_rows = (long long)n_tokens * q_heads;
         const unsigned blocks = (unsigned)((n_rows + 3) / 4);
         if (dtype == MLC_DTYPE_F32)
-            attention_combine_kernel<float><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, (float*)out);
+            attention_combine_kernel<float><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, sinks, q_heads, (float*)out);
         else
-            attention_combine_kernel<bf16><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, (bf16*)out);
+            attention_combine_kernel<bf16><<<blocks, 128, 0, s>>>(part_ml, part_o, n_rows, n_splits, hd, sinks, q_heads, (bf16*)out);
         MLC_LAUNCH_CHECK();
     }
     return 0;
@@ -296,32 +301,33 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
 #ifndef MLC_KERNELS_ONLY   // a file that includes this one for its kernels defines its own entry points
 using namespace mlc;
 
-// q, out: [n_tokens][q_heads][hd] of `dtype`; the cache pools hold the same type.
+// q, out: [n_tokens][q_heads][hd] of `dtype`; the cache pools hold the same type.  sinks: null, or one float per query
+// head whose exponential is added to that head's softmax denominator (a key that is always seen and has no value).
 // max_q_len: the longest sequence of this step (sizes the grid).  n_splits > 1 needs
 // part_ml (n_tokens*q_heads*n_splits*2 floats) and part_o (n_tokens*q_heads*n_splits*hd).
 extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int* cu_seqlens,
                                   const int* start_pos, int n_seqs, int n_tokens, int max_q_len, int q_heads,
                                   int kv_heads, int hd, float scale, int window, int n_splits, float* part_ml,
                                   float* part_o, void* k_pool, void* v_pool, const int* page_table,
-                                  long long entry_offset, int pages_per_seq, int page_size, void* stream) {
+                                  long long entry_offset, int pages_per_seq, int page_size, const float* sinks, void* stream) {
     return launch_attention_simt(q, out, dtype, cu_seqlens, start_pos, n_seqs, n_tokens, max_q_len, q_heads, kv_heads, hd,
                                  scale, window, n_splits, part_ml, part_o, k_pool, v_pool, page_table, entry_offset,
-                                 pages_per_seq, page_size, (cudaStream_t)stream);
+                                 pages_per_seq, page_size, (cudaStream_t)stream, sinks);
 }
 
 // Merge partial results that another attention kernel left in part_ml / part_o
 // (maxima in natural-log units, sums and weighted values relative to them).
 extern "C" int mlc_attention_combine(const float* part_ml, const float* part_o, long long n_rows, int n_splits,
-                                     int hd, void* out, int dtype, void* stream) {
+                                     int hd, const float* sinks, int q_heads, void* out, int dtype, void* stream) {
     if (n_rows <= 0) return 0;
-    if (n_splits < 1 || hd <= 0) return MLC_ERR_BAD_SIZE;
+    if (n_splits < 1 || hd <= 0 || (sinks != nullptr && q_heads <= 0)) return MLC_ERR_BAD_SIZE;
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == MLC_DTYPE_F32)
-        e = launch_pdl(attention_combine_kernel<float>, dim3(blocks), dim3(128), 0, s, part_ml, part_o, n_rows, n_splits, hd, (float*)out);
+        e = launch_pdl(attention_combine_kernel<float>, dim3(blocks), dim3(128), 0, s, part_ml, part_o, n_rows, n_splits, hd, sinks, q_heads, (float*)out);
     else if (dtype == MLC_DTYPE_BF16)
-        e = launch_pdl(attention_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, s, part_ml, part_o, n_rows, n_splits, hd, (bf16*)out);
+        e = launch_pdl(attention_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, s, part_ml, part_o, n_rows, n_splits, hd, sinks, q_heads, (bf16*)out);
     else
         return MLC_ERR_BAD_DTYPE;
     return e == cudaSuccess ? 0 : (int)e;

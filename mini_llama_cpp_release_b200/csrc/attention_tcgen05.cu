@@ -56,6 +56,7 @@ struct TcAttnArgs {
     int heads_per_block, tokens_per_block, head_chunks;
     int window;
     float scale_log2;
+    const float* sinks;         // [q_heads] or null: exp(sinks[h]) joins head h's softmax denominator once, with no value
     int* status;
     long long* timing;          // optional [blocks][16] clock cycles the first softmax warp spent in each phase (0-4), the
                                 // block's tiles (7), cycles from entry to the role's start (14) and end (15); or null
@@ -413,6 +414,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             f[u] = (n_tiles > u) ? fast_exp2(ml[(u * 128 + r) * 2] - m_ref) : 0.0f;
             l_all += (n_tiles > u) ? ml[(u * 128 + r) * 2 + 1] * f[u] : 0.0f;
         }
+        if (a.sinks != nullptr && row_ok) l_all += fast_exp2(a.sinks[kvh * a.group + hg] * 1.4426950408889634f - m_ref);
         const float inv = 1.0f / l_all;
         // runs of 16 columns: two teams take half of them each; three teams (64 columns) take 2, 1 and 1
         constexpr int RUNS = A_HD / 16;
@@ -475,7 +477,8 @@ using namespace mlc;
 extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seqlens, const int* start_pos, int n_seqs,
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
                                      int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                     int pages_per_seq, int page_size, long long pool_pages, long long* timing, void* stream) {
+                                     int pages_per_seq, int page_size, long long pool_pages, long long* timing, const float* sinks,
+                                     void* stream) {
 #if MLC_ATTENTION_TCGEN05
     if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
     if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
@@ -498,6 +501,7 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
     a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.status = status;
+    a.sinks = sinks;
     a.timing = timing;
     if (a.tokens_per_block > 256 || a.heads_per_block > 256) return MLC_ERR_BAD_SIZE;
 

@@ -169,15 +169,16 @@ static cudaError_t launch_rmsnorm_warp(int nv, float* x, const float* delta, int
 }
 
 // ------------------------------------------------------------------ rotation table
-// table[p][i] = (cos(p·f_i), sin(p·f_i)), the angle formed in float32 from an integer
-// position and a float32 frequency, as src/ops.cpp:132-134 does for each token.
-__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int n_pos, int half,
+// table[p][i] = factor · (cos(p·f_i), sin(p·f_i)), the angle formed in float32 from an integer
+// position and a float32 frequency, as src/ops.cpp:132-134 does for each token (factor 1 there;
+// stretched rotations put a constant on both).
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int n_pos, int half, float factor,
                                   float2* __restrict__ table) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)n_pos * half) return;
     const int p = (int)(idx / half), i = (int)(idx % half);
     const float angle = (float)p * inv_freq[i];
-    table[idx] = make_float2(cosf(angle), sinf(angle));
+    table[idx] = make_float2(cosf(angle) * factor, sinf(angle) * factor);
 }
 
 // ------------------------------------------------------------------ Q/K/V epilogue
@@ -319,6 +320,111 @@ __global__ void convert_kernel(const TIn* __restrict__ in, long long total, TOut
     if (idx < total) out[idx] = from_float<TOut>(to_float(in[idx]));
 }
 
+// ------------------------------------------------------------------ layer norm (gain, no bias)
+// LN(v) = (v - mean(v)) / sqrt(mean((v - mean)²) + eps) · w, statistics in float32 in two passes (the mean first,
+// then the squared deviations).  A block per row; the row waits in shared memory between the passes.
+//
+// ln_mode 0, "norm of the stream":   x += sum of the delta slices (if any);  out = LN(x)            (out in T)
+// ln_mode 1, "norm of the branch":   x += LN(sum of the y slices);           out = x, if asked for  (out in T)
+template <typename T>
+__global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict__ y, int n_slices, long long slice_stride,
+                                 const float* __restrict__ gain, float eps, int d, int ln_mode, T* __restrict__ out) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const long long base = (long long)blockIdx.x * d;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = (ln_mode == 0) ? x[base + i] : 0.0f;
+        if (y != nullptr)
+            for (int s = 0; s < n_slices; ++s) v += __ldg(y + s * slice_stride + base + i);
+        if (ln_mode == 0 && y != nullptr) x[base + i] = v;
+        row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float c = row[i] - mean;
+        sq += c * c;
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = (row[i] - mean) * rstd * gain[i];
+        if (ln_mode == 0) {
+            out[base + i] = from_float<T>(v);
+        } else {
+            const float nx = x[base + i] + v;
+            x[base + i] = nx;
+            if (out != nullptr) out[base + i] = from_float<T>(nx);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ per-head RMS norm, partial rotation, cache write
+// Rows of a projection in float32: q heads (H x dim) at q_col, k heads (KV x dim) at k_col, v heads (KV x vdim) at
+// v_col.  q and k: each head divided by its root mean square over dim (eps inside the root) and multiplied by a gain
+// shared by the heads (if given); then the first rot_dims entries of the head are rotated, entry i with entry
+// i + rot_dims/2, by the token's row of the table ([positions][rot_dims/2] cos and sin, any factor on them already
+// applied); the rest pass.  v is multiplied by v_scale.  q goes to q_out [token][head][D], k and v into the token's
+// place in the cache, whose heads have D >= max(dim, vdim) entries: what lies beyond a head's own size is zero, which
+// changes neither a score nor an output.  A warp per head.
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(const float* __restrict__ proj, long long stride, int q_col, int k_col, int v_col,
+                                          const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                                          const int* __restrict__ positions, const int* __restrict__ tok_seq,
+                                          const float2* __restrict__ rope, int rope_positions, int rot_dims, int q_heads,
+                                          int kv_heads_in_row, int dim, int vdim, int D, float v_scale, T* __restrict__ q_out,
+                                          PagedKV cache) {
+    const int n = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const float* row = proj + (long long)n * stride;
+    const int p = positions[n];
+    const int seq = tok_seq[n];
+    const int half = rot_dims >> 1;
+    const float2* cs = (rope != nullptr && half > 0) ? rope + (long long)min(p, rope_positions - 1) * half : nullptr;
+    const int n_heads = q_heads + 2 * kv_heads_in_row;
+    for (int head = warp; head < n_heads; head += n_warps) {
+        if (head < q_heads + kv_heads_in_row) {
+            const bool is_q = head < q_heads;
+            const float* src = row + (is_q ? q_col + head * dim : k_col + (head - q_heads) * dim);
+            const float* gain = is_q ? q_gain : k_gain;
+            T* dst = is_q ? q_out + ((long long)n * q_heads + head) * D
+                          : (T*)cache.k_pool + paged_offset(cache, seq, p, head - q_heads);
+            float ss = 0.0f;
+            for (int i = lane; i < dim; i += 32) ss += src[i] * src[i];
+            ss = warp_sum(ss);
+            const float f = eps >= 0.0f ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;      // a negative eps: no norm
+            for (int i = lane; i < D; i += 32) {
+                float v = 0.0f;
+                if (i < dim) {
+                    v = gain != nullptr ? src[i] * f * gain[i] : src[i] * f;
+                    if (cs != nullptr && i < rot_dims) {
+                        const int j = i < half ? i : i - half;
+                        const int partner = i < half ? i + half : i - half;
+                        const float w = gain != nullptr ? src[partner] * f * gain[partner] : src[partner] * f;
+                        const float2 t = cs[j];
+                        v = i < half ? v * t.x - w * t.y : v * t.x + w * t.y;
+                    }
+                }
+                dst[i] = from_float<T>(v);
+            }
+        } else {
+            const int vh = head - q_heads - kv_heads_in_row;
+            const float* src = row + v_col + vh * vdim;
+            T* dst = (T*)cache.v_pool + paged_offset(cache, seq, p, vh);
+            for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(i < vdim ? src[i] * v_scale : 0.0f);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ soft cap: v <- c · tanh(v / c)
+__global__ void softcap_kernel(float* __restrict__ v, long long total, float cap) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) v[idx] = cap * tanhf(v[idx] / cap);
+}
+
 static inline int row_threads(int d) {
     int t = 32;
     while (t < d && t < 256) t <<= 1;
@@ -380,10 +486,74 @@ extern "C" int mlc_add_rmsnorm(float* x, const float* delta, int n_slices, const
     return 0;
 }
 
-extern "C" int mlc_rope_table(const float* inv_freq, int n_pos, int half, void* table, void* stream) {
+// ln_mode 0: x += sum of the n_slices slices of y (if y is given), out = LN(x)·gain in out_dtype.
+// ln_mode 1: x += LN(sum of the slices of y)·gain; out (may be null) = the new x in out_dtype.
+extern "C" int mlc_layernorm(float* x, const float* y, int n_slices, const float* gain, float eps, int n, int d, int ln_mode,
+                             void* out, int out_dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || d > 32768 || (y != nullptr && n_slices < 1) || (ln_mode != 0 && ln_mode != 1)) return MLC_ERR_BAD_SIZE;
+    if ((ln_mode == 1 && y == nullptr) || (ln_mode == 0 && out == nullptr)) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long stride = (long long)n * d;
+    const size_t smem = (size_t)d * sizeof(float);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e1 = cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        cudaError_t e2 = cudaFuncSetAttribute(layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        if (e1 != cudaSuccess) return (int)e1;
+        if (e2 != cudaSuccess) return (int)e2;
+        raised = true;
+    }
+    cudaError_t e;
+    if (out_dtype == MLC_DTYPE_F32)
+        e = launch_pdl(layernorm_kernel<float>, dim3(n), dim3(row_threads(d)), smem, s, x, y, n_slices, stride, gain, eps, d, ln_mode, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16)
+        e = launch_pdl(layernorm_kernel<bf16>, dim3(n), dim3(row_threads(d)), smem, s, x, y, n_slices, stride, gain, eps, d, ln_mode, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int mlc_qk_norm_rope_cache(const float* proj, long long stride, int q_col, int k_col, int v_col, const float* q_gain,
+                                      const float* k_gain, float eps, const int* positions, const int* tok_seq,
+                                      const void* rope_table, int rope_positions, int rot_dims, int n, int q_heads,
+                                      int kv_heads_in_row, int dim, int vdim, int D, float v_scale, void* q_out, int dtype,
+                                      void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
+                                      int pages_per_seq, int page_size, int cache_kv_heads, void* stream) {
+    if (n <= 0) return 0;
+    if (dim <= 0 || vdim <= 0 || D < dim || D < vdim || q_heads <= 0 || kv_heads_in_row < 0) return MLC_ERR_BAD_SIZE;
+    if (rot_dims < 0 || (rot_dims & 1) || rot_dims > dim) return MLC_ERR_BAD_SIZE;
+    if (kv_heads_in_row != 0 && kv_heads_in_row != cache_kv_heads) return MLC_ERR_BAD_SIZE;
+    PagedKV c{k_pool, v_pool, page_table, entry_offset, pages_per_seq, page_size, cache_kv_heads, D};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int heads = q_heads + 2 * kv_heads_in_row;
+    const int threads = 32 * (heads < 8 ? heads : 8);
+    if (dtype == MLC_DTYPE_F32)
+        qk_norm_rope_cache_kernel<float><<<n, threads, 0, s>>>(proj, stride, q_col, k_col, v_col, q_gain, k_gain, eps, positions,
+                                                               tok_seq, (const float2*)rope_table, rope_positions, rot_dims, q_heads,
+                                                               kv_heads_in_row, dim, vdim, D, v_scale, (float*)q_out, c);
+    else if (dtype == MLC_DTYPE_BF16)
+        qk_norm_rope_cache_kernel<bf16><<<n, threads, 0, s>>>(proj, stride, q_col, k_col, v_col, q_gain, k_gain, eps, positions,
+                                                              tok_seq, (const float2*)rope_table, rope_positions, rot_dims, q_heads,
+                                                              kv_heads_in_row, dim, vdim, D, v_scale, (bf16*)q_out, c);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_softcap(float* v, long long total, float cap, void* stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.0f)) return MLC_ERR_BAD_SIZE;
+    softcap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(v, total, cap);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_rope_table(const float* inv_freq, int n_pos, int half, float factor, void* table, void* stream) {
     if (n_pos <= 0 || half <= 0) return MLC_ERR_BAD_SIZE;
     const long long total = (long long)n_pos * half;
-    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(inv_freq, n_pos, half,
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(inv_freq, n_pos, half, factor,
                                                                                          (float2*)table);
     MLC_LAUNCH_CHECK();
     return 0;

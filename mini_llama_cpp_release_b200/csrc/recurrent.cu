@@ -1,0 +1,463 @@
+// Mixers that keep a fixed-size state per sequence instead of keys and values: the short
+// causal convolution over time, the gated delta rule, and the gated diagonal linear
+// recurrence (real-gated LRU) with its block-diagonal gates.
+//
+// Everything that enters a recurrence is float32 here, in both engine modes: the inputs of
+// the convolutions, the convolutions themselves, unit norms, decays, gates and the state.
+// A step gives every sequence q_len >= 1 new tokens (cu_seqlens) and a slot; the state of a
+// slot is read at the start of the step and left as it stands after the step's last token, so
+// that the same kernels serve whole prompts, portions of prompts and single decoded tokens.
+// No result depends on which other sequences run in the step.
+#include "common.cuh"
+
+namespace mlc {
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ------------------------------------------------------------------ causal convolution
+// y_t[c] = bias[c] + sum_{j < taps} w[c][taps-1-j] · x_{t-j}[c], x before the sequence's first token being zero; an input
+// bias, if given, is added to every real token's x first (it belongs to the projection that made x, not to the zeros).
+// The last taps-1 inputs of a sequence are its state: state[slot][i][c] is the input at (length - (taps-1) + i).
+// The terms are added in ascending j for every token, wherever its inputs come from.
+struct ConvArgs {
+    const float* x;             // [n_tokens] rows of x_stride floats; the C channels start at the pointer
+    long long x_stride;
+    const float* w;             // [C][taps]
+    const float* bias;          // [C] or null
+    const float* in_bias;       // [C] or null: added to x as it is read
+    float* state;               // slot s: state + s * state_stride, [(taps-1)][C]
+    long long state_stride;
+    const int* slots;           // [n_seqs]
+    const int* cu_seqlens;      // [n_seqs + 1]
+    const int* tok_seq;         // [n_tokens]
+    float* out;                 // [n_tokens] rows of out_stride floats
+    long long out_stride;
+    int C, taps, act;           // act 0: none, 1: silu
+    int n_tokens, n_seqs;
+};
+
+__device__ __forceinline__ float conv_finish(float acc, int act) { return act == 1 ? acc * sigmoid_f(acc) : acc; }
+
+__global__ void conv_out_kernel(ConvArgs a) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)a.n_tokens * a.C) return;
+    const int token = (int)(idx / a.C), c = (int)(idx % a.C);
+    const int seq = a.tok_seq[token];
+    const int t = token - a.cu_seqlens[seq];
+    const float* st = a.state + (long long)a.slots[seq] * a.state_stride;
+    const float* w = a.w + (long long)c * a.taps;
+    float acc = a.bias != nullptr ? a.bias[c] : 0.0f;
+    const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
+    for (int j = 0; j < a.taps; ++j) {
+        const int src = t - j;
+        const float v = src >= 0 ? a.x[(long long)(token - j) * a.x_stride + c] + ib : st[(long long)(a.taps - 1 + src) * a.C + c];
+        acc = fmaf(w[a.taps - 1 - j], v, acc);
+    }
+    a.out[(long long)token * a.out_stride + c] = conv_finish(acc, a.act);
+}
+
+// After conv_out_kernel: the state becomes the last taps-1 inputs of the lengthened sequence.
+__global__ void conv_state_kernel(ConvArgs a) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)a.n_seqs * a.C) return;
+    const int seq = (int)(idx / a.C), c = (int)(idx % a.C);
+    const int first = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - first;
+    float* st = a.state + (long long)a.slots[seq] * a.state_stride;
+    const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
+    for (int i = 0; i < a.taps - 1; ++i) {            // ascending: what is read lies ahead of what was written
+        const int src = q_len - (a.taps - 1) + i;
+        st[(long long)i * a.C + c] = src >= 0 ? a.x[(long long)(first + src) * a.x_stride + c] + ib
+                                              : st[(long long)(i + q_len) * a.C + c];
+    }
+}
+
+// Every sequence brings one token (token b belongs to sequence b): output and state in one pass.
+__global__ void conv_step_kernel(ConvArgs a) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)a.n_seqs * a.C) return;
+    const int token = (int)(idx / a.C), c = (int)(idx % a.C);
+    float* st = a.state + (long long)a.slots[token] * a.state_stride;
+    const float* w = a.w + (long long)c * a.taps;
+    const float cur = a.x[(long long)token * a.x_stride + c] + (a.in_bias != nullptr ? a.in_bias[c] : 0.0f);
+    float acc = a.bias != nullptr ? a.bias[c] : 0.0f;
+    acc = fmaf(w[a.taps - 1], cur, acc);
+    for (int j = 1; j < a.taps; ++j) acc = fmaf(w[a.taps - 1 - j], st[(long long)(a.taps - 1 - j) * a.C + c], acc);
+    for (int i = 0; i + 2 < a.taps; ++i) st[(long long)i * a.C + c] = st[(long long)(i + 1) * a.C + c];
+    if (a.taps >= 2) st[(long long)(a.taps - 2) * a.C + c] = cur;
+    a.out[(long long)token * a.out_stride + c] = conv_finish(acc, a.act);
+}
+
+// ------------------------------------------------------------------ gated delta rule
+// Per head, with a state S [dim][vdim] and, for a token, unit vectors k and q (q also times dim^-1/2), a value row v,
+// a decay g in (0, 1) and a step size beta in (0, 1):
+//     S <- g·S;   u = beta·(v - Sᵀk);   S <- S + k uᵀ;   o = Sᵀq.
+// The columns of S never meet, so a block owns 32 of them for one (sequence, head) and walks the sequence's
+// tokens in order; a column is shared by 4 lanes, each holding every fourth row in registers.  Tokens come in
+// chunks of DR_CHUNK: their q, k rows are staged and normalised in shared memory, their decays and step sizes
+// computed, and then the chunk's steps run without touching global memory but for the outputs.
+constexpr int DR_CHUNK = 16;
+constexpr int DR_COLS = 32;
+
+struct DeltaArgs {
+    const float* qkv;           // rows of qkv_stride floats: q heads at q_col, k heads at k_col (G x dim each), v at v_col (H x vdim)
+    long long qkv_stride;
+    int q_col, k_col, v_col;
+    const float* gates;         // rows of gates_stride floats: step-size logits at b_col (H), decay logits at a_col (H)
+    long long gates_stride;
+    int b_col, a_col;
+    const float* A_log;         // [H]
+    const float* dt_bias;       // [H]
+    float* state;               // slot s: state + s * state_stride, [H][dim][vdim]
+    long long state_stride;
+    const int* slots;
+    const int* cu_seqlens;
+    float* out;                 // [n_tokens][H * vdim]
+    int H, G, dim, vdim;
+    float q_scale;              // dim^-1/2
+};
+
+template <int NI>
+__global__ void __launch_bounds__(128)
+delta_rule_kernel(DeltaArgs a) {
+    constexpr int DP = NI * 4;                      // rows of S a column's four lanes cover
+    __shared__ float ks[DR_CHUNK][DP];
+    __shared__ float qs[DR_CHUNK][DP];
+    __shared__ float vs[DR_CHUNK][DR_COLS];
+    __shared__ float gs[DR_CHUNK], bs[DR_CHUNK];
+
+    const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * DR_COLS;
+    const int kv_head = head / (a.H / a.G);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int part = lane >> 3;                     // which rows: part, part + 4, ...
+    const int col = col0 + warp * 8 + (lane & 7);
+    const bool col_ok = col < a.vdim;
+    const int first = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - first;
+    float* S_glob = a.state + (long long)a.slots[seq] * a.state_stride + (long long)head * a.dim * a.vdim;
+
+    float S[NI];
+#pragma unroll
+    for (int ii = 0; ii < NI; ++ii) {
+        const int i = part + 4 * ii;
+        S[ii] = (col_ok && i < a.dim) ? S_glob[(long long)i * a.vdim + col] : 0.0f;
+    }
+    const float neg_rate = -expf(a.A_log[head]);
+    const float dt_bias = a.dt_bias[head];
+
+    for (int t0 = 0; t0 < q_len; t0 += DR_CHUNK) {
+        const int n_t = min(DR_CHUNK, q_len - t0);
+        __syncthreads();                            // the chunk before has been read
+        for (int idx = tid; idx < DR_CHUNK * DP; idx += 128) {
+            const int t = idx / DP, i = idx % DP;
+            float kv = 0.0f, qv = 0.0f;
+            if (t < n_t && i < a.dim) {
+                const float* row = a.qkv + (long long)(first + t0 + t) * a.qkv_stride;
+                kv = row[a.k_col + kv_head * a.dim + i];
+                qv = row[a.q_col + kv_head * a.dim + i];
+            }
+            ks[t][i] = kv;
+            qs[t][i] = qv;
+        }
+        for (int idx = tid; idx < DR_CHUNK * DR_COLS; idx += 128) {
+            const int t = idx / DR_COLS, j = idx % DR_COLS;
+            float v = 0.0f;
+            if (t < n_t && col0 + j < a.vdim)
+                v = a.qkv[(long long)(first + t0 + t) * a.qkv_stride + a.v_col + head * a.vdim + col0 + j];
+            vs[t][j] = v;
+        }
+        if (tid < DR_CHUNK) {
+            float g = 1.0f, b = 0.0f;
+            if (tid < n_t) {
+                const float* row = a.gates + (long long)(first + t0 + tid) * a.gates_stride;
+                g = expf(neg_rate * softplus_f(row[a.a_col + head] + dt_bias));
+                b = sigmoid_f(row[a.b_col + head]);
+            }
+            gs[tid] = g;
+            bs[tid] = b;
+        }
+        __syncthreads();
+        // unit vectors: a warp per token
+        for (int t = warp; t < n_t; t += 4) {
+            float sk = 0.0f, sq = 0.0f;
+            for (int i = lane; i < a.dim; i += 32) {
+                sk += ks[t][i] * ks[t][i];
+                sq += qs[t][i] * qs[t][i];
+            }
+            sk = warp_sum(sk);
+            sq = warp_sum(sq);
+            const float fk = 1.0f / sqrtf(sk + 1e-6f), fq = a.q_scale / sqrtf(sq + 1e-6f);
+            for (int i = lane; i < a.dim; i += 32) {
+                ks[t][i] *= fk;
+                qs[t][i] *= fq;
+            }
+        }
+        __syncthreads();
+        for (int t = 0; t < n_t; ++t) {
+            const float g = gs[t], beta = bs[t];
+            float dk = 0.0f;
+#pragma unroll
+            for (int ii = 0; ii < NI; ++ii) dk = fmaf(S[ii], ks[t][part + 4 * ii], dk);
+            dk += __shfl_xor_sync(0xffffffffu, dk, 8);
+            dk += __shfl_xor_sync(0xffffffffu, dk, 16);
+            const float u = beta * (vs[t][warp * 8 + (lane & 7)] - g * dk);
+            float dq = 0.0f;
+#pragma unroll
+            for (int ii = 0; ii < NI; ++ii) {
+                S[ii] = fmaf(ks[t][part + 4 * ii], u, g * S[ii]);
+                dq = fmaf(S[ii], qs[t][part + 4 * ii], dq);
+            }
+            dq += __shfl_xor_sync(0xffffffffu, dq, 8);
+            dq += __shfl_xor_sync(0xffffffffu, dq, 16);
+            if (part == 0 && col_ok)
+                a.out[(long long)(first + t0 + t) * a.H * a.vdim + (long long)head * a.vdim + col] = dq;
+        }
+    }
+#pragma unroll
+    for (int ii = 0; ii < NI; ++ii) {
+        const int i = part + 4 * ii;
+        if (col_ok && i < a.dim) S_glob[(long long)i * a.vdim + col] = S[ii];
+    }
+}
+
+// ------------------------------------------------------------------ gated RMS norm of each head's output
+// out[t][h][d] = o / sqrt(mean_d(o²) + eps) · w[d] · silu(gate[t][h][d]); a warp per (token, head).
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+                                     const float* __restrict__ w, float eps, long long n_rows, int H, int vdim,
+                                     T* __restrict__ out) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long token = row / H;
+    const int head = (int)(row % H);
+    const float* src = o + row * vdim;
+    const float* g = gate + token * gate_stride + (long long)head * vdim;
+    float ss = 0.0f;
+    for (int d = lane; d < vdim; d += 32) ss += src[d] * src[d];
+    ss = warp_sum(ss);
+    const float f = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int d = lane; d < vdim; d += 32) {
+        const float z = g[d];
+        out[row * vdim + d] = from_float<T>(src[d] * f * w[d] * (z * sigmoid_f(z)));
+    }
+}
+
+// ------------------------------------------------------------------ gates of the diagonal recurrence
+// The channels are cut into B blocks of bw; in block b: r = sigmoid(Wr[b]·u_b + br), i = sigmoid(Wi[b]·u_b + bi),
+// then per channel a = exp(-c·r·softplus(lam)) and drive = sqrt(1 - a²)·i·u.  Both products are float32
+// multiply-adds, each output one accumulator over ascending k, so a token's gates do not depend on the batch.
+// Tiles of 64 tokens x 64 channels, 4 x 4 per thread and gate.
+struct GateArgs {
+    const float* u;             // [n][W]
+    const float* wr;            // [B][bw][bw] (out, in)
+    const float* wi;
+    const float* br;            // [W]
+    const float* bi;            // [W]
+    const float* lam;           // [W]
+    float* a_out;               // [n][W]
+    float* drive_out;           // [n][W]
+    int n, W, bw;
+    float c;
+};
+
+__global__ void __launch_bounds__(256)
+block_gates_kernel(GateArgs a) {
+    __shared__ float Us[16][68];
+    __shared__ float Rs[16][68];
+    __shared__ float Is[16][68];
+    const int tok0 = blockIdx.x * 64, out0 = blockIdx.y * 64, blk = blockIdx.z;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float* wr = a.wr + (long long)blk * a.bw * a.bw;
+    const float* wi = a.wi + (long long)blk * a.bw * a.bw;
+    float ar[4][4], ai[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ar[i][j] = ai[i][j] = 0.0f;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;          // the row (token or output channel) and first k this thread stages
+    for (int k0 = 0; k0 < a.bw; k0 += 16) {
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = k0 + lk + e;
+            const bool k_ok = k < a.bw;
+            const int tok = tok0 + lr, oc = out0 + lr;
+            Us[lk + e][lr] = (k_ok && tok < a.n) ? a.u[(long long)tok * a.W + blk * a.bw + k] : 0.0f;
+            Rs[lk + e][lr] = (k_ok && oc < a.bw) ? wr[(long long)oc * a.bw + k] : 0.0f;
+            Is[lk + e][lr] = (k_ok && oc < a.bw) ? wi[(long long)oc * a.bw + k] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float uv[4], rv[4], iv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) uv[i] = Us[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                rv[j] = Rs[k][tx * 4 + j];
+                iv[j] = Is[k][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ar[i][j] = fmaf(uv[i], rv[j], ar[i][j]);
+                    ai[i][j] = fmaf(uv[i], iv[j], ai[i][j]);
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int tok = tok0 + ty * 4 + i;
+        if (tok >= a.n) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int oc = out0 + tx * 4 + j;
+            if (oc >= a.bw) continue;
+            const int ch = blk * a.bw + oc;
+            const float r = sigmoid_f(ar[i][j] + a.br[ch]);
+            const float gi = sigmoid_f(ai[i][j] + a.bi[ch]);
+            const float av = expf(-a.c * r * softplus_f(a.lam[ch]));
+            const long long at = (long long)tok * a.W + ch;
+            a.a_out[at] = av;
+            a.drive_out[at] = sqrtf(1.0f - av * av) * gi * a.u[at];
+        }
+    }
+}
+
+// ------------------------------------------------------------------ the diagonal recurrence itself
+// S_t = a_t·S_{t-1} + drive_t per channel; out_t = S_t · gelu_tanh(y_t + y_bias) · out_scale.  A thread per
+// (sequence, channel) walks the sequence's tokens; the loads of four tokens are issued together.
+template <typename T>
+__global__ void linear_scan_kernel(const float* __restrict__ av, const float* __restrict__ drive, const float* __restrict__ y,
+                                   long long y_stride, const float* __restrict__ y_bias, float* state, long long state_stride,
+                                   const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int W, float out_scale,
+                                   T* __restrict__ out) {
+    const int seq = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int first = cu_seqlens[seq], last = cu_seqlens[seq + 1];
+    float* st = state + (long long)slots[seq] * state_stride + c;
+    float S = *st;
+    const float yb = y_bias != nullptr ? y_bias[c] : 0.0f;
+    int t = first;
+    for (; t + 4 <= last; t += 4) {
+        float a4[4], d4[4], y4[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            a4[e] = av[(long long)(t + e) * W + c];
+            d4[e] = drive[(long long)(t + e) * W + c];
+            y4[e] = y[(long long)(t + e) * y_stride + c];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            S = fmaf(a4[e], S, d4[e]);
+            out[(long long)(t + e) * W + c] = from_float<T>(S * gelu_tanh_f(y4[e] + yb) * out_scale);
+        }
+    }
+    for (; t < last; ++t) {
+        S = fmaf(av[(long long)t * W + c], S, drive[(long long)t * W + c]);
+        out[(long long)t * W + c] = from_float<T>(S * gelu_tanh_f(y[(long long)t * y_stride + c] + yb) * out_scale);
+    }
+    *st = S;
+}
+
+}  // namespace mlc
+
+using namespace mlc;
+
+// x, out: float32 rows (strides in floats); w float32 [C][taps]; state float32, a slot's [(taps-1)][C] at
+// state + slot * state_stride.  max_q_len == 1 (every sequence one token) runs output and state in one kernel.
+extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* w, const float* bias, const float* in_bias,
+                               int C, int taps, int act,
+                               float* state, long long state_stride, const int* slots, const int* cu_seqlens,
+                               const int* tok_seq, int n_seqs, int n_tokens, int max_q_len, float* out, long long out_stride,
+                               void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (C <= 0 || taps < 1 || taps > 64 || (act != 0 && act != 1)) return MLC_ERR_BAD_SIZE;
+    ConvArgs a{x, x_stride, w, bias, in_bias, state, state_stride, slots, cu_seqlens, tok_seq, out, out_stride, C, taps, act, n_tokens, n_seqs};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (max_q_len == 1 && n_tokens == n_seqs) {
+        conv_step_kernel<<<(unsigned)(((long long)n_seqs * C + 255) / 256), 256, 0, s>>>(a);
+        MLC_LAUNCH_CHECK();
+        return 0;
+    }
+    conv_out_kernel<<<(unsigned)(((long long)n_tokens * C + 255) / 256), 256, 0, s>>>(a);
+    MLC_LAUNCH_CHECK();
+    if (taps > 1) {
+        conv_state_kernel<<<(unsigned)(((long long)n_seqs * C + 255) / 256), 256, 0, s>>>(a);
+        MLC_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+extern "C" int mlc_gated_delta_rule(const float* qkv, long long qkv_stride, int q_col, int k_col, int v_col, const float* gates,
+                                    long long gates_stride, int b_col, int a_col, const float* A_log, const float* dt_bias,
+                                    float* state, long long state_stride, const int* slots, const int* cu_seqlens, int n_seqs,
+                                    int H, int G, int dim, int vdim, float* out, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G != 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535 || H > 65535) return MLC_ERR_BAD_SIZE;
+    DeltaArgs a{qkv, qkv_stride, q_col, k_col, v_col, gates, gates_stride, b_col, a_col, A_log, dt_bias, state, state_stride,
+                slots, cu_seqlens, out, H, G, dim, vdim, 1.0f / sqrtf((float)dim)};
+    const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int ni = (dim + 3) / 4;
+    if (ni <= 8) delta_rule_kernel<8><<<grid, 128, 0, s>>>(a);
+    else if (ni <= 16) delta_rule_kernel<16><<<grid, 128, 0, s>>>(a);
+    else if (ni <= 24) delta_rule_kernel<24><<<grid, 128, 0, s>>>(a);
+    else if (ni <= 32) delta_rule_kernel<32><<<grid, 128, 0, s>>>(a);
+    else if (ni <= 48) delta_rule_kernel<48><<<grid, 128, 0, s>>>(a);
+    else delta_rule_kernel<64><<<grid, 128, 0, s>>>(a);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_gated_rmsnorm(const float* o, const float* gate, long long gate_stride, const float* w, float eps,
+                                 long long n_tokens, int H, int vdim, void* out, int out_dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (H <= 0 || vdim <= 0) return MLC_ERR_BAD_SIZE;
+    const long long n_rows = n_tokens * H;
+    const unsigned blocks = (unsigned)((n_rows + 3) / 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == MLC_DTYPE_F32)
+        gated_rmsnorm_kernel<float><<<blocks, 128, 0, s>>>(o, gate, gate_stride, w, eps, n_rows, H, vdim, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16)
+        gated_rmsnorm_kernel<bf16><<<blocks, 128, 0, s>>>(o, gate, gate_stride, w, eps, n_rows, H, vdim, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_block_gates(const float* u, const float* wr, const float* wi, const float* br, const float* bi,
+                               const float* lam, int n, int W, int B, float c, float* a_out, float* drive_out, void* stream) {
+    if (n <= 0) return 0;
+    if (W <= 0 || B <= 0 || W % B != 0 || B > 65535) return MLC_ERR_BAD_SIZE;
+    const int bw = W / B;
+    GateArgs a{u, wr, wi, br, bi, lam, a_out, drive_out, n, W, bw, c};
+    const dim3 grid((n + 63) / 64, (bw + 63) / 64, B);
+    if (grid.y > 65535) return MLC_ERR_BAD_SIZE;
+    block_gates_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_linear_scan(const float* av, const float* drive, const float* y, long long y_stride, const float* y_bias,
+                               float* state, long long state_stride, const int* slots, const int* cu_seqlens, int n_seqs, int W,
+                               float out_scale, void* out, int out_dtype, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (W <= 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    const dim3 grid((W + 127) / 128, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == MLC_DTYPE_F32)
+        linear_scan_kernel<float><<<grid, 128, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16)
+        linear_scan_kernel<bf16><<<grid, 128, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}

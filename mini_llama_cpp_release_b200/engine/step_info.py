@@ -8,8 +8,8 @@ result.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import List, Optional
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
 
 import torch
 
@@ -29,6 +29,9 @@ class StepInfo:
     want_rows: torch.Tensor       # [n_want] packed token rows whose logits are asked for
     page_tables: List[torch.Tensor]   # per cache group: [n_seqs, pages] page of each page index, -1: none
     slots_long: Optional[torch.Tensor] = None   # [n_seqs] int64 copy of `slots`, for indexing state tensors; None when no mixer of the model declared state
+    # what one part leaves for the next part of the same step (a block that has just written the residual stream's
+    # 16-bit copy hands it to the block that reads it); keyed by the leaving part's choice, gone with the step
+    handover: Dict[str, Any] = field(default_factory=dict)
 
     @property
     def is_decode(self) -> bool:

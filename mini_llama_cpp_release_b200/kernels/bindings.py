@@ -15,6 +15,8 @@ __all__ = [
     "KernelError", "KVView", "require_cuda", "dtype_code", "embed", "add_rmsnorm", "rope_table", "qkv_post",
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
     "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "PinnedCopy", "decode_advance",
+    "layernorm", "qk_norm_rope_cache", "softcap", "convert", "causal_conv", "gated_delta_rule", "gated_rmsnorm", "block_gates",
+    "linear_scan",
 ]
 
 
@@ -87,14 +89,22 @@ def core() -> ctypes.CDLL:
         sigs = {
             "mlc_embed": [P, I, P, I, I, P, P],
             "mlc_add_rmsnorm": [P, P, I, P, F, I, I, P, I, P],
-            "mlc_rope_table": [P, I, I, P, P],
+            "mlc_rope_table": [P, I, I, F, P, P],
+            "mlc_layernorm": [P, P, I, P, F, I, I, I, P, I, P],
+            "mlc_qk_norm_rope_cache": [P, LL, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P, P, LL, I, I, I, P],
+            "mlc_softcap": [P, LL, F, P],
+            "mlc_causal_conv": [P, LL, P, P, P, I, I, I, P, LL, P, P, P, I, I, I, P, LL, P],
+            "mlc_gated_delta_rule": [P, LL, I, I, I, P, LL, I, I, P, P, P, LL, P, P, I, I, I, I, I, P, P],
+            "mlc_gated_rmsnorm": [P, P, LL, P, F, LL, I, I, P, I, P],
+            "mlc_block_gates": [P, P, P, P, P, P, I, I, I, F, P, P, P],
+            "mlc_linear_scan": [P, P, P, LL, P, P, LL, P, P, I, I, F, P, I, P],
             "mlc_qkv_post": [P, P, P, P, P, I, I, I, I, I, P, I, P, P, P, LL, I, I, I, P],
             "mlc_silu_mul": [P, I, I, I, I, P, I, P],
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
-            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P],
+            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P, LL, I, P],
-            "mlc_attention_combine": [P, P, LL, I, I, P, I, P],
+            "mlc_attention_combine": [P, P, LL, I, I, P, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_pair": [P, P, P, I, I, I, I, I, I, I, P, I, P],
@@ -184,13 +194,13 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tens
                                   dtype_code(out.dtype), _stream()), "rmsnorm")
 
 
-def rope_table(inv_freq: torch.Tensor, n_pos: int) -> torch.Tensor:
-    """[n_pos][half][2] float32: cos and sin of position * inv_freq, the angle in float32."""
+def rope_table(inv_freq: torch.Tensor, n_pos: int, factor: float = 1.0) -> torch.Tensor:
+    """[n_pos][half][2] float32: `factor` times cos and sin of position * inv_freq, the angle in float32."""
     require_cuda(inv_freq)
     assert inv_freq.dtype == torch.float32
     half = inv_freq.numel()
     table = torch.empty((n_pos, half, 2), dtype=torch.float32, device=inv_freq.device)
-    _check(core().mlc_rope_table(inv_freq.data_ptr(), n_pos, half, table.data_ptr(), _stream()), "rope table")
+    _check(core().mlc_rope_table(inv_freq.data_ptr(), n_pos, half, float(factor), table.data_ptr(), _stream()), "rope table")
     return table
 
 
@@ -219,10 +229,12 @@ def qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.T
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                    n_seqs: int, max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int = 0,
                    n_splits: int = 1, part_ml: Optional[torch.Tensor] = None,
-                   part_o: Optional[torch.Tensor] = None) -> None:
-    require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o)
+                   part_o: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
+    """`sinks`: None, or float32 [q_heads]: exp(sinks[h]) joins the softmax denominator of head h (once, with no value)."""
+    require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o, sinks)
     n_tokens = q.shape[0]
     assert q.dtype == out.dtype == kv.k_pool.dtype
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == q_heads)
     if n_splits > 1:
         assert part_ml is not None and part_ml.numel() >= n_tokens * q_heads * n_splits * 2
         assert part_o is not None and part_o.numel() >= n_tokens * q_heads * n_splits * kv.head_dim
@@ -230,7 +242,7 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor,
                                      start_pos.data_ptr(), n_seqs, n_tokens, max_q_len, q_heads, kv.kv_heads,
                                      kv.head_dim, float(scale), int(window), n_splits, _ptr(part_ml), _ptr(part_o),
                                      kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
-                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _stream()), "attention")
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _ptr(sinks), _stream()), "attention")
     if n_splits > 1:
         count_launches(1)
 
@@ -326,6 +338,158 @@ def decode_advance(chosen: torch.Tensor, tokens: torch.Tensor, positions: torch.
            "decode advance")
 
 
+
+def layernorm(x: torch.Tensor, y: Optional[torch.Tensor], gain: torch.Tensor, eps: float, out: Optional[torch.Tensor],
+              of_branch: bool) -> None:
+    """Layer norm with a gain and no bias, statistics in float32.  `of_branch` False: x (float32 [n, d]) += y if given
+    ([n, d] or slices [s, n, d] that are added up), out = LN(x).  `of_branch` True: x += LN(y); out, if given, receives
+    the new x in its own type."""
+    require_cuda(x, y, gain, out)
+    n, d = x.shape
+    assert x.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == d
+    assert out is None or out.shape == x.shape
+    n_slices = 1
+    if y is not None:
+        assert y.dtype == torch.float32 and tuple(y.shape[-2:]) == (n, d)
+        n_slices = y.shape[0] if y.dim() == 3 else 1
+    _check(core().mlc_layernorm(x.data_ptr(), _ptr(y), n_slices, gain.data_ptr(), float(eps), n, d, 1 if of_branch else 0,
+                                _ptr(out), dtype_code(out.dtype) if out is not None else 0, _stream()), "layer norm")
+
+
+def qk_norm_rope_cache(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_gain: Optional[torch.Tensor],
+                       k_gain: Optional[torch.Tensor], eps: float, positions: torch.Tensor, tok_seq: torch.Tensor,
+                       rope: Optional[torch.Tensor], rot_dims: int, q_heads: int, kv_heads_in_row: int, dim: int, vdim: int,
+                       v_scale: float, q_out: torch.Tensor, kv: Optional[KVView]) -> None:
+    """Rows of a float32 projection (q heads at column q_col, k heads at k_col, v heads at v_col): per-head RMS norm of q
+    and k (gain optional; a negative eps: none), rotation of the first `rot_dims` entries of each head by the table
+    `rope` [positions, rot_dims/2, 2], v times `v_scale`; q into q_out [n, q_heads, D], k and v into the cache, whose
+    heads have D >= max(dim, vdim) entries (the rest zero)."""
+    require_cuda(proj, q_gain, k_gain, positions, tok_seq, rope, q_out)
+    n = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.dim() == 2
+    D = q_out.numel() // max(1, n * q_heads)
+    assert q_out.numel() == n * q_heads * D
+    assert rope is None or (rope.dtype == torch.float32 and rope.shape[1] * 2 == rot_dims)
+    if kv_heads_in_row:
+        assert kv is not None and kv.k_pool.dtype == q_out.dtype and kv.head_dim == D
+        args = (kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset,
+                kv.pages_per_seq, kv.page_size, kv.kv_heads)
+    else:
+        args = (None, None, None, 0, 0, 1, 0)
+    _check(core().mlc_qk_norm_rope_cache(proj.data_ptr(), proj.stride(0), q_col, k_col, v_col, _ptr(q_gain), _ptr(k_gain),
+                                         float(eps), positions.data_ptr(), tok_seq.data_ptr(), _ptr(rope),
+                                         rope.shape[0] if rope is not None else 0, rot_dims if rope is not None else 0, n,
+                                         q_heads, kv_heads_in_row, dim, vdim, D, float(v_scale), q_out.data_ptr(),
+                                         dtype_code(q_out.dtype), *args, _stream()), "q/k norm, rotation and cache write")
+
+
+def softcap(values: torch.Tensor, cap: float) -> None:
+    """values (float32, in place) <- cap * tanh(values / cap)."""
+    require_cuda(values)
+    assert values.dtype == torch.float32
+    _check(core().mlc_softcap(values.data_ptr(), values.numel(), float(cap), _stream()), "soft cap")
+
+
+def convert(src: torch.Tensor, out: torch.Tensor) -> None:
+    """out = src in out's element type (float32 to bfloat16 or back)."""
+    require_cuda(src, out)
+    assert src.numel() == out.numel()
+    _check(core().mlc_convert(src.data_ptr(), dtype_code(src.dtype), src.numel(), out.data_ptr(), dtype_code(out.dtype),
+                              _stream()), "conversion")
+
+
+def _columns(t: torch.Tensor, col: int) -> int:
+    """Address of column `col` of the float32 row-major matrix `t`."""
+    assert t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1
+    return t.data_ptr() + 4 * col
+
+
+def _require_rows(t: torch.Tensor) -> None:
+    """A float32 matrix on the device whose rows are dense (it may be a column range of a wider one)."""
+    if not t.is_cuda:
+        raise KernelError("this engine runs on a CUDA device only: got a tensor on " + str(t.device))
+    if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"expected float32 rows, got {t.dtype} with shape {tuple(t.shape)} and strides {t.stride()}")
+
+
+def causal_conv(x: torch.Tensor, col: int, weight: torch.Tensor, bias: Optional[torch.Tensor], silu: bool,
+                state: torch.Tensor, step, out: torch.Tensor, in_bias: Optional[torch.Tensor] = None) -> None:
+    """Per-channel causal convolution over time of the C channels of x (float32 rows) that start at column `col`:
+    weight float32 [C, taps], the last tap on the current token; `state` float32 [slots, (taps-1)*C] holds every
+    sequence's last taps-1 inputs (rows of (taps-1)*C floats) and is brought up to date; `in_bias` [C], if given, is
+    added to x as it is read; out float32 [n, C] (csrc/recurrent.cu)."""
+    require_cuda(weight, bias, in_bias, out)
+    _require_rows(state)
+    C, taps = weight.shape
+    n = x.shape[0]
+    assert weight.dtype == torch.float32 and out.dtype == torch.float32
+    assert out.shape == (n, C) and col + C <= x.shape[1] and state.shape[1] == (taps - 1) * C
+    for b in (bias, in_bias):
+        assert b is None or (b.dtype == torch.float32 and b.numel() == C)
+    _check(core().mlc_causal_conv(_columns(x, col), x.stride(0), weight.data_ptr(), _ptr(bias), _ptr(in_bias), C, taps,
+                                  1 if silu else 0,
+                                  state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(),
+                                  step.tok_seq.data_ptr(), step.n_seqs, n, step.max_q_len, out.data_ptr(), out.stride(0),
+                                  _stream()), "causal convolution")
+    if step.max_q_len > 1 and taps > 1:
+        count_launches(1)
+
+
+def gated_delta_rule(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor, b_col: int, a_col: int,
+                     A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, step, heads: int, kv_heads: int,
+                     dim: int, vdim: int, out: torch.Tensor) -> None:
+    """The gated delta rule over the step's tokens (csrc/recurrent.cu): q, k (kv_heads x dim) and v (heads x vdim) in the
+    float32 rows `qkv`, step-size and decay logits (heads each) in the float32 rows `gates`; `state` float32
+    [slots, heads, dim, vdim]; out float32 [n, heads * vdim]."""
+    require_cuda(A_log, dt_bias, out)
+    _require_rows(state)
+    n = qkv.shape[0]
+    assert A_log.dtype == dt_bias.dtype == out.dtype == torch.float32
+    assert state.shape[1] == heads * dim * vdim and out.shape == (n, heads * vdim)
+    _check(core().mlc_gated_delta_rule(_columns(qkv, 0), qkv.stride(0), q_col, k_col, v_col, _columns(gates, 0),
+                                       gates.stride(0), b_col, a_col, A_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(),
+                                       state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs,
+                                       heads, kv_heads, dim, vdim, out.data_ptr(), _stream()), "gated delta rule")
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, gate_col: int, gain: torch.Tensor, eps: float, heads: int,
+                  vdim: int, out: torch.Tensor) -> None:
+    """out[t, h, :] = o[t, h, :] / rms · gain · silu(gate[t, gate_col + h*vdim + :]) per head (o float32 [n, heads*vdim])."""
+    require_cuda(o, gain, out)
+    n = o.shape[0]
+    assert o.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == vdim and out.shape == o.shape
+    _check(core().mlc_gated_rmsnorm(o.data_ptr(), _columns(gate, gate_col), gate.stride(0), gain.data_ptr(), float(eps), n,
+                                    heads, vdim, out.data_ptr(), dtype_code(out.dtype), _stream()), "gated head norm")
+
+
+def block_gates(u: torch.Tensor, w_r: torch.Tensor, w_i: torch.Tensor, b_r: torch.Tensor, b_i: torch.Tensor,
+                lam: torch.Tensor, c: float, a_out: torch.Tensor, drive_out: torch.Tensor) -> None:
+    """Gates of the diagonal recurrence from u (float32 [n, W]) with block-diagonal weights [B, W/B, W/B]:
+    a = exp(-c · sigmoid(Wr u + br) · softplus(lam)), drive = sqrt(1 - a²) · sigmoid(Wi u + bi) · u."""
+    require_cuda(u, w_r, w_i, b_r, b_i, lam, a_out, drive_out)
+    n, W = u.shape
+    B = w_r.shape[0]
+    assert all(t.dtype == torch.float32 for t in (u, w_r, w_i, b_r, b_i, lam, a_out, drive_out))
+    assert w_r.shape == w_i.shape == (B, W // B, W // B) and a_out.shape == drive_out.shape == u.shape
+    _check(core().mlc_block_gates(u.data_ptr(), w_r.data_ptr(), w_i.data_ptr(), b_r.data_ptr(), b_i.data_ptr(),
+                                  lam.data_ptr(), n, W, B, float(c), a_out.data_ptr(), drive_out.data_ptr(), _stream()),
+           "recurrence gates")
+
+
+def linear_scan(a: torch.Tensor, drive: torch.Tensor, y: torch.Tensor, y_col: int, y_bias: Optional[torch.Tensor],
+                state: torch.Tensor, step, out_scale: float, out: torch.Tensor) -> None:
+    """S_t = a_t · S_{t-1} + drive_t per channel from each sequence's `state` (float32 [slots, W], left at the last
+    token's value); out = S · gelu_tanh(y[:, y_col:y_col+W] + y_bias) · out_scale."""
+    require_cuda(a, drive, y_bias, out)
+    _require_rows(state)
+    n, W = a.shape
+    assert a.dtype == drive.dtype == torch.float32 and out.shape == (n, W) and state.shape[1] == W
+    _check(core().mlc_linear_scan(a.data_ptr(), drive.data_ptr(), _columns(y, y_col), y.stride(0), _ptr(y_bias),
+                                  state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(),
+                                  step.n_seqs, W, float(out_scale), out.data_ptr(), dtype_code(out.dtype), _stream()),
+           "linear recurrence")
+
+
 class PinnedCopy:
     """dst ← src on the current stream, one of them in pinned host memory and the other on the device, both dense and of
     one type and size: the few hundred bytes a decode step brings and takes.  Checked once, when it is made; a call
@@ -372,12 +536,12 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     if lib is None:
         lib = _build.attention_library(head_dim)
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
-        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, I, P, P]
+        lib.mlc_attention_mma.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P, P, LL, I, I, I, P, P, P]
         lib.mlc_attention_mma.restype = c_int
         lib.mlc_attention_mma_head_dim.restype = c_int
         lib.mlc_attention_decode_clusters_resident.argtypes = [I]
         lib.mlc_attention_decode_clusters_resident.restype = c_int
-        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P]
+        lib.mlc_attention_tcgen05.argtypes = [P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P, LL, I, I, LL, P, P, P]
         lib.mlc_attention_tcgen05.restype = c_int
         if lib.mlc_attention_mma_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.mlc_attention_mma_head_dim()}, wanted {head_dim}")
@@ -455,11 +619,12 @@ def attention_tcgen05_blocks(max_q_len: int, n_seqs: int, q_heads: int, kv_heads
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                       max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int,
-                      ) -> None:
+                      sinks: Optional[torch.Tensor] = None) -> None:
     """Prompt attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry on the tcgen05 tensor cores
     (head sizes 64 and 128, pages of 64 tokens).  Keys are not shared out over blocks: meant for steps whose rows fill
     the GPU; a block itself works on two key tiles at a time."""
-    require_cuda(q, out, cu_seqlens, start_pos)
+    require_cuda(q, out, cu_seqlens, start_pos, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == q_heads)
     if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the tcgen05 attention takes bfloat16 queries, cache and output")
     lib = attention_library(kv.head_dim)
@@ -467,16 +632,18 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tens
     _check(lib.mlc_attention_tcgen05(q.data_ptr(), out.data_ptr(), cu_seqlens.data_ptr(), start_pos.data_ptr(), n_seqs,
                                      q.shape[0], max_q_len, q_heads, kv.kv_heads, kv.head_dim, float(scale), int(window),
                                      status.data_ptr(), kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
-                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], None, _stream()),
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, kv.k_pool.shape[1], None, _ptr(sinks),
+                                     _stream()),
            "tcgen05 attention")
 
 
 def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, n_seqs: int,
                   max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int, row_tiles: int, n_splits: int,
                   part_ml: Optional[torch.Tensor] = None, part_o: Optional[torch.Tensor] = None,
-                  warp_private: bool = True) -> None:
-    """Tensor-core attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry."""
-    require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o)
+                  warp_private: bool = True, sinks: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention of bfloat16 q [n, q_heads*hd] over a bfloat16 cache entry (`sinks` as for `attention_simt`)."""
+    require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == q_heads)
     if q.dtype != torch.bfloat16 or kv.k_pool.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16 queries and cache")
     n_tokens = q.shape[0]
@@ -490,11 +657,13 @@ def attention_mma(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, 
                                  n_tokens, max_q_len, q_heads, kv.kv_heads, hd, float(scale), int(window), row_tiles,
                                  1 if warp_private else 0, n_splits, _ptr(part_ml), _ptr(part_o), kv.k_pool.data_ptr(),
                                  kv.v_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq,
-                                 kv.page_size, int(kv.k_pool.shape[1]), gemm_status(q.device).data_ptr(), _stream()),
+                                 kv.page_size, int(kv.k_pool.shape[1]), gemm_status(q.device).data_ptr(), _ptr(sinks),
+                                 _stream()),
            "tensor-core attention")
     if n_splits > 1 and not in_cluster:
         _check(core().mlc_attention_combine(part_ml.data_ptr(), part_o.data_ptr(), n_tokens * q_heads, n_splits, hd,
-                                            out.data_ptr(), dtype_code(out.dtype), _stream()), "attention combine")
+                                            _ptr(sinks), q_heads, out.data_ptr(), dtype_code(out.dtype), _stream()),
+               "attention combine")
 
 
 EPI_STORE, EPI_SILU_MUL, EPI_QKV, EPI_ADD = 0, 1, 2, 3

@@ -1,6 +1,8 @@
 """The parts models are assembled from.  Importing this package registers the built-in
-kinds: norm/rmsnorm, position/rope_neox, position/none, mixer/gqa_attention,
-feed_forward/swiglu, block/prenorm, embedding/token_embedding, head/linear_head."""
+kinds: norm/rmsnorm, norm/layernorm, position/rope_neox, position/rope_partial, position/none,
+mixer/gqa_attention, mixer/sink_attention, mixer/gated_delta, mixer/gated_linear_recurrence,
+mixer/parallel, feed_forward/swiglu, block/prenorm, block/branch_norm, embedding/token_embedding,
+head/linear_head."""
 from .base import CacheNeed, MixerMemory, Part, Runtime, StateSpec, TensorSpec  # noqa: F401
 from .linear import Linear  # noqa: F401
-from . import norm, rotary, attention, feed_forward, block, embedding  # noqa: F401
+from . import norm, rotary, attention, recurrent, feed_forward, block, embedding  # noqa: F401

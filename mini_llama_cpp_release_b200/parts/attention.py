@@ -161,6 +161,7 @@ class GQAttention(Part):
         """Attention of the step's tokens over the cache entry `kv` (which already holds their keys)."""
         rt = self.runtime
         window = self.window or 0
+        sinks = getattr(self, "sinks", None)          # float32 [heads] or None: a logit per head that joins every softmax
         if self.use_tensor_cores:
             row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
                                                              self.KV, rt.n_sms)
@@ -168,7 +169,7 @@ class GQAttention(Part):
                     and kernels.attention_tcgen05_takes(self.hd, kv.page_size, self.H, self.KV)):
                 # prompts whose rows fill the GPU without sharing out the keys: the tcgen05 kernel
                 kernels.attention_tcgen05(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                                          self.scale, window)
+                                          self.scale, window, sinks=sinks)
                 return
             part_ml = part_o = None
             if step.max_q_len == 1 and row_tiles == 1:
@@ -179,7 +180,7 @@ class GQAttention(Part):
                 part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
                 part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
             kernels.attention_mma(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                                  self.scale, window, row_tiles, n_splits, part_ml, part_o)
+                                  self.scale, window, row_tiles, n_splits, part_ml, part_o, sinks=sinks)
             return
         n_splits = choose_splits(step, self.H, self.KV, rt.n_sms, tokens_per_block=max(1, 16 // min(16, self.H // self.KV)))
         part_ml = part_o = None
@@ -187,7 +188,7 @@ class GQAttention(Part):
             part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
             part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
         kernels.attention_simt(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                               self.scale, window, n_splits, part_ml, part_o)
+                               self.scale, window, n_splits, part_ml, part_o, sinks=sinks)
 
 
 def choose_splits(step, q_heads: int, kv_heads: int, n_sms: int, tokens_per_block: int, keys_per_split: int = 256,
@@ -201,3 +202,126 @@ def choose_splits(step, q_heads: int, kv_heads: int, n_sms: int, tokens_per_bloc
     by_fill = (2 * n_sms + blocks - 1) // blocks
     by_len = max(1, step.max_kv_len // keys_per_split)
     return max(1, min(by_fill, by_len, max_splits))
+
+
+def fused_rows(weights, runtime) -> Linear:
+    """One `Linear` over several matrices that read the same input, their rows stacked in order; rows of zeros bring
+    the count to a multiple of 16, which the tensor-core products of prompts want."""
+    w = torch.cat(list(weights), dim=0)
+    pad = (-w.shape[0]) % 16
+    if pad:
+        w = torch.cat([w, torch.zeros(pad, w.shape[1], dtype=w.dtype, device=w.device)], dim=0)
+    return Linear(w, runtime)
+
+
+@register_part("mixer", "sink_attention")
+class SinkAttention(GQAttention):
+    """Grouped-query attention whose softmax has a sink: per head a learned logit that joins the denominator once, with
+    no key and no value, outside the scale.  Queries and keys are normalised per head (RMS over the head, a gain shared
+    by the heads) before they are rotated; keys and queries have `head_dim` entries, values `v_head_dim`; the score's
+    scale is a parameter.  No biases.
+
+        q = rot(rms(W_q h)·g_q), k = rot(rms(W_k h)·g_k), v = W_v h
+        p_ij = exp(scale·q_i·k_j) / (exp(sink) + sum_{j' <= i} exp(scale·q_i·k_j')),   out = W_o (p v)
+
+    In the cache and in the kernels a head has D = max(head_dim, v_head_dim) entries, rounded up to 16; what lies
+    beyond a head's own size is zero (and the output projection has zero columns there).  `value_scale` multiplies
+    the values as they are stored, which multiplies the attention's output (an arrangement that adds this mixer to
+    another with a factor passes the factor here, so that it acts in float32 before anything is rounded).
+
+    `names`: the tensors' names below the part's prefix, by role (q, k, v, o, q_norm, k_norm, sink).  Offers
+    `in_weights()` and `mix()` to an arrangement that computes several mixers' input projections in one product."""
+    graph_safe = True
+    accumulates = False
+
+    NAMES = dict(q="q", k="k", v="v", o="o", q_norm="q.norm", k_norm="k.norm", sink="sink")
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
+                 scale: float, norm_eps: float, position: PartSpec, qk_norm: bool = True, sink: bool = True,
+                 window: Optional[int] = None, value_scale: float = 1.0, names: Optional[dict] = None):
+        Part.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                      v_head_dim=v_head_dim, scale=scale, norm_eps=norm_eps, qk_norm=qk_norm, sink=sink, window=window,
+                      value_scale=value_scale)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
+        self.hidden, self.H, self.KV = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dim, self.vdim = int(head_dim), int(v_head_dim)
+        self.hd = (max(self.dim, self.vdim) + 15) // 16 * 16          # a head's size in the cache and the kernels
+        if self.hd > 256:
+            raise ValueError(f"attention: head sizes up to 256 are supported, got {max(self.dim, self.vdim)}")
+        if not scale > 0:
+            raise ValueError(f"attention: the score's scale must be positive, got {scale}")
+        self.scale, self.eps = float(scale), float(norm_eps)
+        self.qk_norm, self.has_sink = bool(qk_norm), bool(sink)
+        self.window = int(window) if window else None
+        self.value_scale = float(value_scale)
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+        self.position = build_part(position, name)
+        self.sinks: Optional[torch.Tensor] = None
+
+    def tensors(self):
+        t = self.t
+        specs = [TensorSpec(t["q"], (self.H * self.dim, self.hidden)), TensorSpec(t["k"], (self.KV * self.dim, self.hidden)),
+                 TensorSpec(t["v"], (self.KV * self.vdim, self.hidden)), TensorSpec(t["o"], (self.hidden, self.H * self.vdim))]
+        if self.qk_norm:
+            specs += [TensorSpec(t["q_norm"], (self.dim,), role="gain", init="one_plus_normal"),
+                      TensorSpec(t["k_norm"], (self.dim,), role="gain", init="one_plus_normal")]
+        if self.has_sink:
+            specs.append(TensorSpec(t["sink"], (self.H,), role="bias"))
+        return specs
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("window" if self.window else "all", self.KV, self.hd, self.window)
+
+    def bind(self, get, runtime):
+        Part.bind(self, get, runtime)
+        t = self.t
+        self._in = [get(t["q"]), get(t["k"]), get(t["v"])]
+        self.in_proj: Optional[Linear] = None
+        self.q_gain = get(t["q_norm"]).to(torch.float32).contiguous() if self.qk_norm else None
+        self.k_gain = get(t["k_norm"]).to(torch.float32).contiguous() if self.qk_norm else None
+        self.sinks = get(t["sink"]).to(torch.float32).contiguous() if self.has_sink else None
+        wo = get(t["o"])
+        if self.hd != self.vdim:            # the kernels' heads are wider than the values: columns of zeros
+            padded = torch.zeros(self.hidden, self.H, self.hd, dtype=wo.dtype, device=wo.device)
+            padded[:, :, :self.vdim] = wo.view(self.hidden, self.H, self.vdim)
+            wo = padded.view(self.hidden, self.H * self.hd)
+        self.o = Linear(wo, runtime)
+        self.use_tensor_cores = runtime.dtype == torch.bfloat16
+        if self.use_tensor_cores:
+            kernels.attention_library(self.hd)
+
+    def in_weights(self):
+        """The matrices that read the mixer's input, in the order of the columns `mix` expects."""
+        return list(self._in)
+
+    def in_width(self) -> int:
+        return (self.H + self.KV) * self.dim + self.KV * self.vdim
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in self._in) + self.o.nbytes()
+
+    def mix(self, proj: torch.Tensor, col: int, step, memory: MixerMemory) -> torch.Tensor:
+        """Attention from the float32 projection rows `proj`, whose columns from `col` on are [q | k | v]; returns the
+        heads' outputs [n, heads·D] in the engine's type, the input of `self.o`."""
+        rt = self.runtime
+        n = proj.shape[0]
+        table = self.position.table_for(step.max_kv_len) if hasattr(self.position, "table_for") else None
+        rot = getattr(self.position, "dims", 0) if table is not None else 0
+        kv_heads = self.KV if memory.writes_cache else 0
+        q = rt.empty(n, self.H * self.hd)
+        q_col = col
+        k_col = q_col + self.H * self.dim
+        v_col = k_col + self.KV * self.dim
+        kernels.qk_norm_rope_cache(proj, q_col, k_col, v_col, self.q_gain, self.k_gain, self.eps if self.qk_norm else -1.0,
+                                   step.positions, step.tok_seq, table, rot, self.H, kv_heads, self.dim, self.vdim,
+                                   self.value_scale, q, memory.kv if memory.writes_cache else None)
+        o = rt.empty(n, self.H * self.hd)
+        self.attend(q, o, step, memory.kv)
+        return o
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
+        if self.in_proj is None:
+            self.in_proj = fused_rows(self._in, self.runtime)
+        o = self.mix(self.in_proj(h, torch.float32), 0, step, memory)
+        return self.o(o, torch.float32, partial_ok=True)

@@ -11,6 +11,7 @@ from typing import Optional, Tuple
 
 import torch
 
+from .. import kernels
 from ..config.registry import register_part, build_part
 from ..config.specs import PartSpec
 from .base import MixerMemory, Part
@@ -42,3 +43,61 @@ class PreNormBlock(Part):
         h2 = self.feed_forward_norm.forward(x, a)
         f = ffn.forward(h2, step, residual=x) if getattr(ffn, "accumulates", False) else ffn.forward(h2, step)
         return x, f
+
+
+@register_part("block", "branch_norm")
+class BranchNormBlock(Part):
+    """Norm on each branch's output only: x ← x + norm(mixer(x)); x ← x + norm(feed_forward(x)).  The branches read
+    the stream itself.  The feed-forward (with its norm) may be absent.
+
+    The stream is float32.  An engine that computes in 16 bits gives the branches a 16-bit copy of it: the kernel
+    that adds a normalised branch writes the copy of the new stream as well, and leaves it in the step's
+    `handover` for whoever reads the stream next (the block's own feed-forward, or the next block of this kind);
+    only a block that finds no copy there makes one."""
+    graph_safe = True
+
+    COPY = "stream_copy"
+
+    def __init__(self, name: str, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: Optional[PartSpec] = None,
+                 feed_forward_norm: Optional[PartSpec] = None, names: Optional[dict] = None):
+        super().__init__(name)
+        names = names or {}
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("branch_norm block: a feed-forward and its norm come together or not at all")
+        self.mixer = build_part(mixer, name + names.get("mixer", "mixer."))
+        self.mixer_norm = build_part(mixer_norm, name + names.get("mixer_norm", "mixer_norm."))
+        self.feed_forward = build_part(feed_forward, name + names.get("feed_forward", "feed_forward.")) if feed_forward else None
+        self.feed_forward_norm = (build_part(feed_forward_norm, name + names.get("feed_forward_norm", "feed_forward_norm."))
+                                  if feed_forward_norm else None)
+
+    def children(self):
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm) if p is not None)
+
+    def _input(self, x: torch.Tensor, step) -> torch.Tensor:
+        """What a branch reads: the stream itself in a float32 engine, else its copy in the engine's type."""
+        rt = self.runtime
+        if rt.dtype == torch.float32:
+            return x
+        left = step.handover.pop(self.COPY, None)
+        if left is not None and left[0] is x:
+            return left[1]
+        h = rt.empty(*x.shape)
+        kernels.convert(x, h)
+        return h
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], step, memory: MixerMemory
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        rt = self.runtime
+        if pending is not None:                     # a block of another kind left a branch output to be added
+            x.add_(pending.sum(dim=0) if pending.dim() == 3 else pending)
+        copy_dtype = None if rt.dtype == torch.float32 else rt.dtype
+        y = self.mixer.forward(self._input(x, step), step, memory)
+        h = self.mixer_norm.add_normed(x, y, copy_dtype)
+        if h is not None:
+            step.handover[self.COPY] = (x, h)
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(self._input(x, step), step)
+            h = self.feed_forward_norm.add_normed(x, f, copy_dtype)
+            if h is not None:
+                step.handover[self.COPY] = (x, h)
+        return x, None

@@ -17,16 +17,18 @@ from .linear import Linear
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int):
-        super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size)
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, tensor: str = "weight"):
+        """`tensor`: the table's name below the part's prefix."""
+        super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size, tensor=tensor)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+        self.tensor = self.name + tensor
 
     def tensors(self):
-        return [TensorSpec(self.name + "weight", (self.vocab, self.hidden), role="table")]
+        return [TensorSpec(self.tensor, (self.vocab, self.hidden), role="table")]
 
     def bind(self, get, runtime):
         super().bind(get, runtime)
-        self.table = get(self.name + "weight").contiguous()
+        self.table = get(self.tensor).contiguous()
 
     def weight_bytes(self) -> int:
         return 0      # a step touches one row per token, not the table
@@ -41,24 +43,33 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     graph_safe = True
 
-    def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
-        super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to)
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
+                 tensor: str = "weight", softcap: Optional[float] = None):
+        """`tensor`: the matrix's name below the part's prefix.  `softcap` c: logits ← c·tanh(logits / c), in float32."""
+        super().__init__(name, vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to, tensor=tensor, softcap=softcap)
         self.vocab, self.hidden, self.tied_to = int(vocab_size), int(hidden_size), tied_to
+        self.tensor = self.name + tensor
+        self.softcap = float(softcap) if softcap else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"head: the soft cap must be positive, got {softcap}")
 
     def tensors(self):
         if self.tied_to:
             return [TensorSpec(self.tied_to, (self.vocab, self.hidden), role="table", stored=False)]
-        return [TensorSpec(self.name + "weight", (self.vocab, self.hidden))]
+        return [TensorSpec(self.tensor, (self.vocab, self.hidden))]
 
     def ignorable_tensors(self):
-        return [self.name + "weight"] if self.tied_to else []
+        return [self.tensor] if self.tied_to else []
 
     def bind(self, get, runtime):
         super().bind(get, runtime)
-        self.proj = Linear(get(self.tied_to or (self.name + "weight")), runtime)
+        self.proj = Linear(get(self.tied_to or self.tensor), runtime)
 
     def weight_bytes(self) -> int:
         return self.proj.nbytes()
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.proj(h, torch.float32)
+        logits = self.proj(h, torch.float32)
+        if self.softcap is not None:
+            kernels.softcap(logits, self.softcap)
+        return logits

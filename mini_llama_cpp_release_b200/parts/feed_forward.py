@@ -3,6 +3,8 @@
 [Wgate; Wup]; the activation and the product are one kernel."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import kernels
@@ -17,24 +19,28 @@ from .linear import Linear
 class SwiGLU(Part):
     graph_safe = True
 
-    def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "silu"):
-        super().__init__(name, hidden_size=hidden_size, intermediate_size=intermediate_size, activation=activation)
+    def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: Optional[dict] = None):
+        """`names`: the three matrices' names below the part's prefix, by role ("gate", "up", "down")."""
+        super().__init__(name, hidden_size=hidden_size, intermediate_size=intermediate_size, activation=activation, names=names)
+        names = names or {}
+        self.t_gate = name + names.get("gate", "gate_proj.weight")
+        self.t_up = name + names.get("up", "up_proj.weight")
+        self.t_down = name + names.get("down", "down_proj.weight")
         if activation != "silu":
             raise ValueError(f"feed-forward: only the silu activation is supported (src/ops.cpp:94-107), got {activation!r}")
         self.hidden, self.inter = int(hidden_size), int(intermediate_size)
 
     def tensors(self):
-        n = self.name
         return [
-            TensorSpec(n + "gate_proj.weight", (self.inter, self.hidden)),
-            TensorSpec(n + "up_proj.weight", (self.inter, self.hidden)),
-            TensorSpec(n + "down_proj.weight", (self.hidden, self.inter)),
+            TensorSpec(self.t_gate, (self.inter, self.hidden)),
+            TensorSpec(self.t_up, (self.inter, self.hidden)),
+            TensorSpec(self.t_down, (self.hidden, self.inter)),
         ]
 
     def bind(self, get, runtime):
         super().bind(get, runtime)
-        n = self.name
-        gate, up = get(n + "gate_proj.weight"), get(n + "up_proj.weight")
+        gate, up = get(self.t_gate), get(self.t_up)
         # The fused product (SiLU·mul inside the tcgen05 kernel's epilogue) wants gate_j and up_j on
         # neighbouring rows: g0, u0, g1, u1, ...  Otherwise the rows are [gate; up].
         self.fused = runtime.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 \
@@ -44,7 +50,7 @@ class SwiGLU(Part):
         else:
             w = torch.cat([gate, up], dim=0)
         self.gate_up = Linear(w, runtime)
-        self.down = Linear(get(n + "down_proj.weight"), runtime)
+        self.down = Linear(get(self.t_down), runtime)
 
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()

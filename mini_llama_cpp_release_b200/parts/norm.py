@@ -41,3 +41,43 @@ class RMSNorm(Part):
         out = self.runtime.empty(*x.shape, dtype=out_dtype or self.runtime.dtype)
         kernels.add_rmsnorm(x, delta, self.gain, self.eps, out)
         return out
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """Layer norm with a gain and no bias: (v - mean) / sqrt(var + eps) · w, var the mean of the squared deviations,
+    statistics in float32.  Two uses: `forward`, the norm of the stream (as `RMSNorm.forward`: adds `delta` first),
+    and `add_normed`, for arrangements that normalise a branch's output before it joins the stream.  `tensor` is the
+    gain's name below the part's prefix."""
+    graph_safe = True
+
+    def __init__(self, name: str, size: int, eps: float, tensor: str = "weight"):
+        super().__init__(name, size=size, eps=eps, tensor=tensor)
+        self.size = int(size)
+        self.eps = float(eps)
+        self.tensor = self.name + tensor
+
+    def tensors(self):
+        return [TensorSpec(self.tensor, (self.size,), role="gain", init="one_plus_normal")]
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        self.gain = get(self.tensor).to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.gain.numel() * 4
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x: float32 [n, size], updated in place to x + delta when delta is given; returns LN(x)."""
+        out = self.runtime.empty(*x.shape, dtype=out_dtype or self.runtime.dtype)
+        kernels.layernorm(x, delta, self.gain, self.eps, out, of_branch=False)
+        return out
+
+    def add_normed(self, x: torch.Tensor, y: torch.Tensor, copy_dtype: Optional[torch.dtype] = None
+                   ) -> Optional[torch.Tensor]:
+        """x (float32 [n, size], in place) += LN(y), y float32 [n, size] or slices [s, n, size] that are added up first.
+        With `copy_dtype`, also returns the new x in that type (the next part's input)."""
+        out = self.runtime.empty(*x.shape, dtype=copy_dtype) if copy_dtype is not None else None
+        kernels.layernorm(x, y, self.gain, self.eps, out, of_branch=True)
+        return out

@@ -1,0 +1,254 @@
+"""Mixers that keep a fixed-size state per sequence: the gated delta rule, the gated diagonal
+linear recurrence, and the arrangement that runs two mixers side by side on one input.
+
+What they share: every matrix that reads the mixer's input is a row range of one product
+(`fused_rows`), whose float32 output the kernels of csrc/recurrent.cu read by column; whatever
+enters a recurrence stays float32 in both engine modes (convolution inputs and outputs, unit
+norms, decays, gates, the state); the state of a sequence is one row of float32 per slot, cut
+into the pieces a mixer needs, zero when the slot is taken and carried from step to step.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import kernels
+from ..config.registry import build_part, register_part
+from ..config.specs import PartSpec
+from .attention import fused_rows
+from .base import MixerMemory, Part, StateSpec, TensorSpec
+from .linear import Linear
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+@register_part("mixer", "gated_delta")
+class GatedDeltaMixer(Part):
+    """The gated delta rule (Yang, Kautz, Hatamizadeh, "Gated Delta Networks: Improving Mamba2 with Delta Rule").
+
+        q, k = W_q h, W_k h (kv_heads x dim);  v = W_v h (heads x vdim);  head n reads q/k head n // (heads/kv_heads)
+        each of q, k, v: causal convolution over time per channel (`conv` taps, no bias), then silu
+        q, k: unit vectors per head, x / sqrt(sum x² + 1e-6);  q also times dim^-1/2
+        beta = sigmoid(W_b h),  g = exp(-exp(A_log) · softplus(W_a h + dt_bias))           (one per head)
+        per head:  S ← g S;  u = beta (v - Sᵀk);  S ← S + k uᵀ;  o = Sᵀq
+        out = W_o ( o / rms(o) · w_norm · silu(W_g h) )                                      (rms over vdim, per head)
+
+    State per sequence: S [heads, dim, vdim] and the last conv-1 inputs of the convolutions, all float32.
+    `names`: the tensors' names below the part's prefix, by role."""
+    graph_safe = True
+
+    NAMES = dict(q="q", k="k", v="v", q_conv="q.conv", k_conv="k.conv", v_conv="v.conv", b="b", a="a", g="g", o="o",
+                 A_log="A_log", dt_bias="dt_bias", norm="norm")
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
+                 conv: int, norm_eps: float, names: Optional[dict] = None):
+        super().__init__(name, hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                         v_head_dim=v_head_dim, conv=conv, norm_eps=norm_eps)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"gated delta rule: {num_heads} heads are not a multiple of {num_kv_heads} q/k heads")
+        if not 1 <= head_dim <= 256:
+            raise ValueError(f"gated delta rule: q/k head sizes up to 256 are supported, got {head_dim}")
+        if conv < 1:
+            raise ValueError("gated delta rule: the convolution needs at least one tap")
+        self.hidden, self.H, self.G = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dim, self.vdim, self.taps, self.eps = int(head_dim), int(v_head_dim), int(conv), float(norm_eps)
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+        self.n_qk, self.n_v = self.G * self.dim, self.H * self.vdim
+        self.n_conv = 2 * self.n_qk + self.n_v                       # channels that pass the convolution: q | k | v
+        self.n_S = self.H * self.dim * self.vdim
+
+    def tensors(self):
+        t, hid = self.t, self.hidden
+        return [TensorSpec(t["q"], (self.n_qk, hid)), TensorSpec(t["k"], (self.n_qk, hid)), TensorSpec(t["v"], (self.n_v, hid)),
+                TensorSpec(t["q_conv"], (self.n_qk, self.taps)), TensorSpec(t["k_conv"], (self.n_qk, self.taps)),
+                TensorSpec(t["v_conv"], (self.n_v, self.taps)),
+                TensorSpec(t["b"], (self.H, hid)), TensorSpec(t["a"], (self.H, hid)), TensorSpec(t["g"], (self.n_v, hid)),
+                TensorSpec(t["A_log"], (self.H,), role="bias"), TensorSpec(t["dt_bias"], (self.H,), role="bias"),
+                TensorSpec(t["norm"], (self.vdim,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["o"], (hid, self.n_v))]
+
+    def cache_need(self):
+        return None
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.n_S + (self.taps - 1) * self.n_conv,), torch.float32)
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        t = self.t
+        # columns of the input product: q | k | v | g | b | a
+        self.in_proj = fused_rows([get(t[r]) for r in ("q", "k", "v", "g", "b", "a")], runtime)
+        self.g_col = self.n_conv
+        self.b_col = self.g_col + self.n_v
+        self.a_col = self.b_col + self.H
+        self.conv_w = _f32(torch.cat([get(t["q_conv"]), get(t["k_conv"]), get(t["v_conv"])], dim=0))
+        self.A_log, self.dt_bias, self.gain = _f32(get(t["A_log"])), _f32(get(t["dt_bias"])), _f32(get(t["norm"]))
+        self.o = Linear(get(t["o"]), runtime)
+
+    def weight_bytes(self) -> int:
+        return self.in_proj.nbytes() + self.o.nbytes() + self.conv_w.numel() * 4
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory) -> torch.Tensor:
+        rt = self.runtime
+        n = h.shape[0]
+        proj = self.in_proj(h, torch.float32)
+        S, conv_state = memory.state[:, :self.n_S], memory.state[:, self.n_S:]
+        qkv = rt.empty(n, self.n_conv, dtype=torch.float32)
+        kernels.causal_conv(proj, 0, self.conv_w, None, True, conv_state, step, qkv)
+        o = rt.empty(n, self.n_v, dtype=torch.float32)
+        kernels.gated_delta_rule(qkv, 0, self.n_qk, 2 * self.n_qk, proj, self.b_col, self.a_col, self.A_log, self.dt_bias,
+                                 S, step, self.H, self.G, self.dim, self.vdim, o)
+        act = rt.empty(n, self.n_v)
+        kernels.gated_rmsnorm(o, proj, self.g_col, self.gain, self.eps, self.H, self.vdim, act)
+        return self.o(act, torch.float32, partial_ok=True)
+
+
+@register_part("mixer", "gated_linear_recurrence")
+class GatedLinearRecurrence(Part):
+    """The recurrent block of Griffin (De et al., "Griffin: Mixing Gated Linear Recurrences with Local Attention for
+    Efficient Language Models") with its real-gated linear recurrent unit.  Two branches of `width` channels:
+
+        y = gelu_tanh(W_y h + b_y);   u = conv(W_x h + b_x)        (causal, per channel, `conv` taps, with a bias)
+        in each of `blocks` equal parts of the channels:  r = sigmoid(R u + b_r),  i = sigmoid(I u + b_i)
+        a = exp(-c · r · softplus(lam)),  c = 8;   S_t = a S_{t-1} + sqrt(1 - a²) · i · u;   out = W_o (S · y)
+
+    State per sequence: S [width] and the convolution's last conv-1 inputs, float32.  `out_scale` multiplies S·y in
+    float32 before it is rounded for the output product.  Offers `in_weights()` and `mix()` like the attention."""
+    graph_safe = True
+
+    DECAY_CONSTANT = 8.0
+
+    NAMES = dict(y="y", y_bias="y.b", x="x", x_bias="x.b", conv="conv", conv_bias="conv.b", r="ra", r_bias="ra.b", i="ri",
+                 i_bias="ri.b", lam="lam", o="o")
+
+    def __init__(self, name: str, hidden_size: int, width: int, blocks: int, conv: int, out_scale: float = 1.0,
+                 names: Optional[dict] = None):
+        super().__init__(name, hidden_size=hidden_size, width=width, blocks=blocks, conv=conv, out_scale=out_scale)
+        if blocks < 1 or width % blocks:
+            raise ValueError(f"linear recurrence: {width} channels do not divide into {blocks} equal parts")
+        if conv < 1:
+            raise ValueError("linear recurrence: the convolution needs at least one tap")
+        self.hidden, self.W, self.B, self.taps = int(hidden_size), int(width), int(blocks), int(conv)
+        self.out_scale = float(out_scale)
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+
+    def tensors(self):
+        t, W, bw = self.t, self.W, self.W // self.B
+        return [TensorSpec(t["y"], (W, self.hidden)), TensorSpec(t["y_bias"], (W,), role="bias"),
+                TensorSpec(t["x"], (W, self.hidden)), TensorSpec(t["x_bias"], (W,), role="bias"),
+                TensorSpec(t["conv"], (W, self.taps)), TensorSpec(t["conv_bias"], (W,), role="bias"),
+                TensorSpec(t["r"], (self.B, bw, bw)), TensorSpec(t["r_bias"], (self.B, bw), role="bias"),
+                TensorSpec(t["i"], (self.B, bw, bw)), TensorSpec(t["i_bias"], (self.B, bw), role="bias"),
+                TensorSpec(t["lam"], (W,), role="bias"), TensorSpec(t["o"], (self.hidden, W))]
+
+    def cache_need(self):
+        return None
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.W * self.taps,), torch.float32)          # S, then taps-1 rows of inputs
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        t = self.t
+        self._in = [get(t["y"]), get(t["x"])]
+        self.in_proj: Optional[Linear] = None
+        self.y_bias, self.x_bias = _f32(get(t["y_bias"])), _f32(get(t["x_bias"]))
+        self.conv_w, self.conv_bias = _f32(get(t["conv"])), _f32(get(t["conv_bias"]))
+        self.w_r, self.w_i = _f32(get(t["r"])), _f32(get(t["i"]))
+        self.b_r, self.b_i = _f32(get(t["r_bias"])).view(-1), _f32(get(t["i_bias"])).view(-1)
+        self.lam = _f32(get(t["lam"]))
+        self.o = Linear(get(t["o"]), runtime)
+
+    def in_weights(self):
+        return list(self._in)
+
+    def in_width(self) -> int:
+        return 2 * self.W
+
+    def weight_bytes(self) -> int:
+        return (sum(w.numel() * w.element_size() for w in self._in) + self.o.nbytes()
+                + 4 * (self.w_r.numel() + self.w_i.numel() + self.conv_w.numel()))
+
+    def mix(self, proj: torch.Tensor, col: int, step, memory: MixerMemory) -> torch.Tensor:
+        """From the float32 projection rows `proj`, whose columns from `col` on are [y | x]: S·y [n, width] in the engine's
+        type, the input of `self.o`."""
+        rt = self.runtime
+        n, W = proj.shape[0], self.W
+        S, conv_state = memory.state[:, :W], memory.state[:, W:]
+        u = rt.empty(n, W, dtype=torch.float32)
+        kernels.causal_conv(proj, col + W, self.conv_w, self.conv_bias, False, conv_state, step, u, in_bias=self.x_bias)
+        a, drive = rt.empty(n, W, dtype=torch.float32), rt.empty(n, W, dtype=torch.float32)
+        kernels.block_gates(u, self.w_r, self.w_i, self.b_r, self.b_i, self.lam, self.DECAY_CONSTANT, a, drive)
+        act = rt.empty(n, W)
+        kernels.linear_scan(a, drive, proj, col, self.y_bias, S, step, self.out_scale, act)
+        return act
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory) -> torch.Tensor:
+        if self.in_proj is None:
+            self.in_proj = fused_rows(self._in, self.runtime)
+        act = self.mix(self.in_proj(h, torch.float32), 0, step, memory)
+        return self.o(act, torch.float32, partial_ok=True)
+
+
+@register_part("mixer", "parallel")
+class ParallelMixer(Part):
+    """Two mixers side by side on the same input: out = left_scale · left(h) + right_scale · right(h).
+
+    Both children offer `in_weights()` (the matrices that read h), `mix(proj, col, step, memory)` (everything between
+    the input product and the output product) and `o` (the output product): the pair's input matrices are one
+    product, and the two output products add up into one float32 result.  The factors reach the children as
+    `value_scale` / `out_scale` parameters (the builder passes them), so they act in float32 inside the children's
+    kernels.  The left child may keep keys and values, the right one a state: the pair asks the cache for both."""
+    graph_safe = True
+
+    def __init__(self, name: str, left: PartSpec, right: PartSpec, names: Optional[dict] = None):
+        super().__init__(name)
+        names = names or {}
+        self.left = build_part(left, name + names.get("left", "left."))
+        self.right = build_part(right, name + names.get("right", "right."))
+        for side, part in (("left", self.left), ("right", self.right)):
+            if not all(hasattr(part, a) for a in ("in_weights", "in_width", "mix")):
+                raise ValueError(f"parallel mixer: the {side} mixer does not offer in_weights / in_width / mix")
+        needs = [p.cache_need() for p in (self.left, self.right) if hasattr(p, "cache_need") and p.cache_need() is not None]
+        states = [p.state_spec() for p in (self.left, self.right) if hasattr(p, "state_spec") and p.state_spec() is not None]
+        if len(needs) > 1 or len(states) > 1:
+            raise ValueError("parallel mixer: at most one child may keep keys and values, and at most one a state")
+
+    def children(self):
+        return (self.left, self.right)
+
+    def cache_need(self):
+        return next((n for n in (p.cache_need() for p in (self.left, self.right)) if n is not None), None)
+
+    def state_spec(self):
+        return next((s for s in (p.state_spec() for p in (self.left, self.right)) if s is not None), None)
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        self.in_proj = fused_rows(self.left.in_weights() + self.right.in_weights(), runtime)
+        self.right_col = self.left.in_width()
+
+    def weight_bytes(self) -> int:
+        return self.left.weight_bytes() + self.right.weight_bytes()
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory) -> torch.Tensor:
+        n = h.shape[0]
+        proj = self.in_proj(h, torch.float32)
+        a_left = self.left.mix(proj, 0, step, memory)
+        a_right = self.right.mix(proj, self.right_col, step, memory)
+        lo, ro = self.left.o, self.right.o
+        if ro.can_add_into_stream(n) and a_right.dtype == torch.bfloat16:
+            out = lo(a_left, torch.float32)
+            ro.add_into(a_right, out)
+            return out
+        out = self.runtime.empty(2, n, lo.out_features, dtype=torch.float32)      # two slices; whoever reads them adds them up
+        if a_left.dtype == torch.float32:
+            kernels.linear_simt(a_left, lo.weight, out[0])
+            kernels.linear_simt(a_right, ro.weight, out[1])
+        else:
+            out[0].copy_(lo(a_left, torch.float32))
+            out[1].copy_(ro(a_right, torch.float32))
+        return out

@@ -94,3 +94,77 @@ class NoPosition(Part):
 
     def prepare(self, n_positions: int) -> None:
         pass
+
+
+def stretched_frequencies(dims: int, base: float, scaling: Optional[dict]) -> Tuple[np.ndarray, float]:
+    """Frequencies of a rotation over `dims` entries, pair i with i + dims/2, f_i = base^(-2i/dims), optionally
+    stretched for contexts longer than the trained one ("YaRN"; Peng et al., "YaRN: Efficient Context Window Extension
+    of Large Language Models"): with scaling = {factor, original, fast, slow},
+
+        turn(t) = dims · ln(original / (2π t)) / (2 ln base)        the pair that makes t turns over `original` positions
+        lo = max(floor(turn(fast)), 0),  hi = min(ceil(turn(slow)), dims - 1)
+        ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+        f'_i = f_i / factor · ramp_i + f_i · (1 - ramp_i)
+
+    so that fast pairs keep their frequency and slow ones are divided by `factor`; cos and sin are both multiplied by
+    0.1 · ln(factor) + 1.  Returns (float32 frequencies [dims/2], that multiplier).  Computed in float64, rounded once."""
+    i = np.arange(dims // 2, dtype=np.float64)
+    f = np.power(float(base), -2.0 * i / dims)
+    if not scaling:
+        return f.astype(np.float32), 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    if factor <= 0 or original <= 0 or float(scaling["fast"]) <= 0 or float(scaling["slow"]) <= 0:
+        raise ValueError("rope scaling: factor, original, fast and slow must be positive")
+
+    def turn(t: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(float(base)))
+    lo = max(math.floor(turn(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(turn(float(scaling["slow"]))), dims - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    f = f / factor * ramp + f * (1.0 - ramp)
+    return f.astype(np.float32), 0.1 * math.log(factor) + 1.0
+
+
+@register_part("position", "rope_partial")
+class RopePartial(Part):
+    """Rotate-half rotation of the first `dims` entries of each head (the rest pass unchanged), with optional
+    stretching of the frequencies (`stretched_frequencies`).  The model gives no largest position, so the table
+    [positions][dims/2] of (cos, sin) grows: it is rebuilt, twice as long, when a step reaches beyond it.  Tables
+    once handed out stay alive and valid for the positions they hold, so a captured graph that reads one keeps
+    reading the same memory; a step is captured for a bound on its positions and asks for its table with that bound."""
+    graph_safe = True
+    fusable = False
+
+    MIN_POSITIONS = 4096
+
+    def __init__(self, name: str, dims: int, base: float, scaling: Optional[dict] = None):
+        super().__init__(name, dims=dims, base=base, scaling=scaling)
+        if dims < 0 or dims % 2:
+            raise ValueError(f"rope: the rotated size must be even and not negative, got {dims}")
+        if not math.isfinite(base) or base <= 0:
+            raise ValueError("rope: base must be finite and positive")
+        self.dims, self.base = int(dims), float(base)
+        self.scaling = dict(scaling) if scaling else None
+        self.table: Optional[torch.Tensor] = None
+        self._old = []                     # tables handed out before the latest one
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        if self.dims:
+            f, self.factor = stretched_frequencies(self.dims, self.base, self.scaling)
+            self.inv_freq = torch.from_numpy(f).to(runtime.device)
+
+    def prepare(self, n_positions: int) -> None:
+        if self.dims == 0 or (self.table is not None and self.table.shape[0] >= n_positions):
+            return
+        size = self.MIN_POSITIONS
+        while size < n_positions:
+            size *= 2
+        if self.table is not None:
+            self._old.append(self.table)
+        self.table = kernels.rope_table(self.inv_freq, size, self.factor)
+
+    def table_for(self, n_positions: int) -> Optional[torch.Tensor]:
+        """The table, holding at least `n_positions` positions (None: nothing is rotated)."""
+        self.prepare(n_positions)
+        return self.table
