@@ -320,10 +320,11 @@ block_gates_kernel(GateArgs a) {
             const int ch = blk * a.bw + oc;
             const float r = sigmoid_f(ar[i][j] + a.br[ch]);
             const float gi = sigmoid_f(ai[i][j] + a.bi[ch]);
-            const float av = expf(-a.c * r * softplus_f(a.lam[ch]));
+            const float log_a = -a.c * r * softplus_f(a.lam[ch]);
             const long long at = (long long)tok * a.W + ch;
-            a.a_out[at] = av;
-            a.drive_out[at] = sqrtf(1.0f - av * av) * gi * a.u[at];
+            a.a_out[at] = expf(log_a);
+            // 1 - a² = -expm1(2 log a): formed from the logarithm, it keeps its digits where a is close to one
+            a.drive_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gi * a.u[at];
         }
     }
 }
