@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--config NAME] [--dtype bfloat16|float32]
     python bench.py --impl reference      # the reference project's own GPU path on the same work
+    python bench.py --compare mepolix-w896 [--layers 6]   # the Mepolix design beside Qwen2 at equal sizes (a line of its own)
 
 A "step" is one decode step of the whole batch.  The default run (`--config qwen2-0.5b`) has the layer sizes of a
 Qwen2-0.5B (24 layers, width 896, 14 query heads on 2 kv heads of size 64, feed-forward 4864, vocabulary 151936,
@@ -42,6 +43,8 @@ CONFIGS = {
     "qwen2-1.5b-ragged16": dict(preset="qwen2-1.5b", prompt_len=2048, ctx_len=4096, ragged=16, max_steps=127),
     "qwen2-7b": dict(preset="qwen2-7b", prompt_len=2048, ctx_len=8192, ragged=None, max_steps=1000),
 }
+# a Mepolix preset → the Qwen2 preset it is timed beside (equal width, attention shape, feed-forward and vocabulary)
+COMPARE = {"mepolix-w896": "qwen2-0.5b", "mepolix-w1536": "qwen2-1.5b", "mepolix-w3584": "qwen2-7b"}
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 REF_SOURCE = os.environ.get("MLC_REFERENCE_SOURCE", "/root/reference")     # where the reference's checkout lies, if baseline/_ref is empty
 REF_PREFILL_TOKENS = 32
@@ -128,6 +131,48 @@ def describe(raw, layers, batch, work) -> dict:
     }
 
 
+# --------------------------------------------------------------------------------------------------- two designs side by side
+def compare(args) -> int:
+    """One JSON line: for the Mepolix preset and its Qwen2 counterpart, with random weights and the same number of
+    layers, a 2,048-token prompt step (device-timed, replayed from its captured graph) and decode steps at batch 8 over
+    2,048-token prompts (device-timed replays of the captured step), with the bytes and operations each has to move."""
+    import mini_llama_cpp_release_b200 as ml
+    from mini_llama_cpp_release_b200 import measure
+    pk = measure.peaks(ROOT)
+    layers = args.layers or 6
+    batch = args.batch or 8
+    prompt_len, ctx_len = args.prompt_len or 2048, 4096
+    steps, warmup = max(1, min(args.steps, 512)), max(3, args.warmup)
+    out = {"compare": args.compare, "layers": layers, "batch": batch, "prompt_len": prompt_len, "dtype": args.dtype,
+           "peaks": pk["source"]}
+    for label, preset in (("mepolix", args.compare), ("qwen2", COMPARE[args.compare])):
+        raw = dict(measure.PRESETS[preset])
+        if "layers" in raw:
+            raw["layers"] = raw["layers"][-layers:]            # ends on a layer with attention beside the recurrence
+        else:
+            raw["num_hidden_layers"] = layers
+        folder = measure.random_model_folder(raw, tag=f"compare_{preset}_L{layers}")
+        llm = ml.load(folder, dtype=args.dtype, max_tokens=batch * ctx_len, max_seqs=batch, max_batch_tokens=16384)
+        vocab = llm.config.vocab_size
+        pre = measure.time_prefill(llm, measure.random_prompts([prompt_len], vocab, seed=77))
+        flops = measure.model_prefill_flops(llm.model, [prompt_len])
+        d = measure.time_decode(llm, measure.random_prompts([prompt_len] * batch, vocab, seed=1), steps, warmup)
+        state_bytes = 2 * batch * sum(t[0].numel() * 4 for t in llm.context.cache.state if t is not None)   # read and written
+        r = measure.roofline(d["step_bytes"] + state_bytes, d["ms_per_step"], pk)
+        out[label] = {
+            "preset": preset, "kinds": [l.get("type") for l in raw["layers"]] if "layers" in raw else None,
+            "prefill_ms": round(pre["ms"], 3), "prefill_tokens_per_s": round(prompt_len / (pre["ms"] / 1e3), 1),
+            "prefill_tflops": round(flops / (pre["ms"] / 1e3) / 1e12, 1),
+            "prefill_frac_of_bf16": round(flops / (pre["ms"] / 1e3) / (pk["bf16_tflops_burst"] * 1e12), 4) if args.dtype == "bfloat16" else None,
+            "decode_ms_per_step": round(d["ms_per_step"], 4), "decode_tokens_per_s": round(d["tokens_per_s"], 1),
+            "decode_launches_per_step": d["launches_per_step"], "decode_library_launches_per_step": d["library_launches_per_step"],
+            "decode_step_bytes": int(d["step_bytes"] + state_bytes), "decode_hbm_frac": r["frac"],
+        }
+        del llm
+    print(json.dumps(out))
+    return 0
+
+
 # --------------------------------------------------------------------------------------------------- our arm
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -143,7 +188,12 @@ def main() -> int:
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run one part only and print a short line (for profiling a small case)")
     ap.add_argument("--prompt-len", type=int, default=None, help="prompt length of the --only runs")
+    ap.add_argument("--compare", default=None, choices=sorted(COMPARE),
+                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix preset beside the Qwen2 "
+                         "preset of the same width, head shape and feed-forward, at --layers layers each (default 6)")
     args = ap.parse_args()
+    if args.compare:
+        return compare(args)
 
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is outside what this library does (single-GPU engine)")

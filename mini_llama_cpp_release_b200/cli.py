@@ -226,7 +226,7 @@ def cmd_bench(argv: Sequence[str]) -> int:
         print(f"decode step:       {step_ms:.4f} ms, {r['achieved']:.1f} GB/s of weights and cache = {r['frac']:.3f} of "
               f"{r['peak']:.0f} GB/s ({pk['source']}); limited by {r['limited_by']}")
     try:
-        flops = measure.prefill_flops(cfg.to_dict(), len(llm.model.spec.schedule), [args.prompt_len] * args.batch)
+        flops = measure.model_prefill_flops(llm.model, [args.prompt_len] * args.batch)
         peak = pk["bf16_tflops_burst"] if llm.model.runtime.dtype == torch.bfloat16 else None
         tf = flops / (prefill_ms / 1e3) / 1e12
         print(f"prompt step:       {tf:.2f} TFLOP/s" + (f" = {tf / peak:.4f} of {peak:.0f} TFLOP/s bf16 ({pk['source']})" if peak else " (float32 arithmetic)"))

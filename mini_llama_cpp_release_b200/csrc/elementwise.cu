@@ -337,8 +337,10 @@ __global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict_
     float sum = 0.0f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = (ln_mode == 0) ? x[base + i] : 0.0f;
-        if (y != nullptr)
+        if (y != nullptr) {
+#pragma unroll 8
             for (int s = 0; s < n_slices; ++s) v += __ldg(y + s * slice_stride + base + i);
+        }
         if (ln_mode == 0 && y != nullptr) x[base + i] = v;
         row[i] = v;
         sum += v;
@@ -360,6 +362,88 @@ __global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict_
             if (out != nullptr) out[base + i] = from_float<T>(nx);
         }
     }
+}
+
+// Many rows: a warp per row, the row in registers from the first load to the last store (NV 16-byte pieces per lane,
+// d <= 128 * NV, d a multiple of 4, all pointers 16-byte aligned); no shared memory and no block-wide barrier.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(float* __restrict__ x, const float* __restrict__ y, int n_slices, long long slice_stride,
+                      const float* __restrict__ gain, float eps, int d, int n, int ln_mode, T* __restrict__ out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const long long base = (long long)row * d;
+    const int d4 = d >> 2;
+    float4* x4 = reinterpret_cast<float4*>(x + base);
+    float4 v[NV], xv[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        xv[k] = (i < d4) ? x4[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        v[k] = (ln_mode == 0) ? xv[k] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (y != nullptr) {
+        for (int s = 0; s < n_slices; ++s) {
+            const float4* t4 = reinterpret_cast<const float4*>(y + s * slice_stride + base);
+#pragma unroll
+            for (int k = 0; k < NV; ++k) {
+                const int i = lane + 32 * k;
+                if (i < d4) {
+                    const float4 t = __ldg(t4 + i);
+                    v[k].x += t.x; v[k].y += t.y; v[k].z += t.z; v[k].w += t.w;
+                }
+            }
+        }
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);      // lanes beyond the row hold zeros
+    const float mean = warp_sum(sum) / (float)d;
+    float sq = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        if (lane + 32 * k < d4) {
+            const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, e = v[k].w - mean;
+            sq += (a * a + b * b) + (c * c + e * e);
+        }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)d + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        if (i >= d4) continue;
+        const float4 g = __ldg(g4 + i);
+        float4 r = make_float4((v[k].x - mean) * rstd * g.x, (v[k].y - mean) * rstd * g.y, (v[k].z - mean) * rstd * g.z,
+                               (v[k].w - mean) * rstd * g.w);
+        if (ln_mode == 0) {
+            if (y != nullptr) x4[i] = v[k];
+        } else {
+            r = make_float4(xv[k].x + r.x, xv[k].y + r.y, xv[k].z + r.z, xv[k].w + r.w);
+            x4[i] = r;
+            if (out == nullptr) continue;
+        }
+        if (sizeof(T) == 4) {
+            reinterpret_cast<float4*>(out + base)[i] = r;
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+            reinterpret_cast<uint2*>(out + base)[i] = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+        }
+    }
+}
+
+template <typename T>
+static cudaError_t launch_layernorm_warp(int nv, float* x, const float* y, int n_slices, long long stride, const float* gain,
+                                         float eps, int d, int n, int ln_mode, T* out, cudaStream_t s) {
+    const dim3 grid((n + 7) / 8), block(256);
+    if (nv <= 1) return launch_pdl(layernorm_warp_kernel<T, 1>, grid, block, 0, s, x, y, n_slices, stride, gain, eps, d, n, ln_mode, out);
+    if (nv <= 2) return launch_pdl(layernorm_warp_kernel<T, 2>, grid, block, 0, s, x, y, n_slices, stride, gain, eps, d, n, ln_mode, out);
+    if (nv <= 4) return launch_pdl(layernorm_warp_kernel<T, 4>, grid, block, 0, s, x, y, n_slices, stride, gain, eps, d, n, ln_mode, out);
+    if (nv <= 8) return launch_pdl(layernorm_warp_kernel<T, 8>, grid, block, 0, s, x, y, n_slices, stride, gain, eps, d, n, ln_mode, out);
+    return launch_pdl(layernorm_warp_kernel<T, 12>, grid, block, 0, s, x, y, n_slices, stride, gain, eps, d, n, ln_mode, out);
 }
 
 // ------------------------------------------------------------------ per-head RMS norm, partial rotation, cache write
@@ -505,12 +589,20 @@ extern "C" int mlc_layernorm(float* x, const float* y, int n_slices, const float
         raised = true;
     }
     cudaError_t e;
+    if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
+    const int nv = ((d >> 2) + 31) / 32;                 // 16-byte pieces per lane if a warp takes a row
+    const bool vec = (d & 3) == 0 && ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)gain) | ((uintptr_t)out)) & 15) == 0;
+    if (vec && nv <= 12 && n >= 128) {
+        e = out_dtype == MLC_DTYPE_F32
+                ? launch_layernorm_warp<float>(nv, x, y, n_slices, stride, gain, eps, d, n, ln_mode, (float*)out, s)
+                : launch_layernorm_warp<bf16>(nv, x, y, n_slices, stride, gain, eps, d, n, ln_mode, (bf16*)out, s);
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    const int threads = norm_threads(d, n);
     if (out_dtype == MLC_DTYPE_F32)
-        e = launch_pdl(layernorm_kernel<float>, dim3(n), dim3(row_threads(d)), smem, s, x, y, n_slices, stride, gain, eps, d, ln_mode, (float*)out);
-    else if (out_dtype == MLC_DTYPE_BF16)
-        e = launch_pdl(layernorm_kernel<bf16>, dim3(n), dim3(row_threads(d)), smem, s, x, y, n_slices, stride, gain, eps, d, ln_mode, (bf16*)out);
+        e = launch_pdl(layernorm_kernel<float>, dim3(n), dim3(threads), smem, s, x, y, n_slices, stride, gain, eps, d, ln_mode, (float*)out);
     else
-        return MLC_ERR_BAD_DTYPE;
+        e = launch_pdl(layernorm_kernel<bf16>, dim3(n), dim3(threads), smem, s, x, y, n_slices, stride, gain, eps, d, ln_mode, (bf16*)out);
     return e == cudaSuccess ? 0 : (int)e;
 }
 

@@ -43,9 +43,8 @@ struct ConvArgs {
 __device__ __forceinline__ float conv_finish(float acc, int act) { return act == 1 ? acc * sigmoid_f(acc) : acc; }
 
 __global__ void conv_out_kernel(ConvArgs a) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long long)a.n_tokens * a.C) return;
-    const int token = (int)(idx / a.C), c = (int)(idx % a.C);
+    const int token = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
     const int seq = a.tok_seq[token];
     const int t = token - a.cu_seqlens[seq];
     const float* st = a.state + (long long)a.slots[seq] * a.state_stride;
@@ -95,10 +94,13 @@ __global__ void conv_step_kernel(ConvArgs a) {
 // Per head, with a state S [dim][vdim] and, for a token, unit vectors k and q (q also times dim^-1/2), a value row v,
 // a decay g in (0, 1) and a step size beta in (0, 1):
 //     S <- g·S;   u = beta·(v - Sᵀk);   S <- S + k uᵀ;   o = Sᵀq.
-// The columns of S never meet, so a block owns 32 of them for one (sequence, head) and walks the sequence's
-// tokens in order; a column is shared by 4 lanes, each holding every fourth row in registers.  Tokens come in
-// chunks of DR_CHUNK: their q, k rows are staged and normalised in shared memory, their decays and step sizes
-// computed, and then the chunk's steps run without touching global memory but for the outputs.
+// The columns of S never meet, so a block owns 32 of them for one (sequence, head) and walks the sequence's tokens in
+// order; a column is shared by 4 lanes, each holding a quarter of its rows in registers.  With the state before the
+// token, S', the token needs two dot products per column that do not wait for each other, and the read-out follows
+// from them:  dk = S'ᵀk,  dq = S'ᵀq,  u = beta·(v - g·dk),  o = g·dq + (k·q)·u,  S = g·S' + k uᵀ.
+// Tokens come in chunks of DR_CHUNK through two shared-memory buffers: while one chunk's steps run, the next
+// chunk's q, k, v rows and gate logits are on their way (cp.async); a chunk that has arrived is prepared in place
+// (unit vectors, k·q, decays, step sizes) and then its steps touch global memory for the outputs only.
 constexpr int DR_CHUNK = 16;
 constexpr int DR_COLS = 32;
 
@@ -120,20 +122,35 @@ struct DeltaArgs {
     float q_scale;              // dim^-1/2
 };
 
+__device__ __forceinline__ void cp_async_f32(float* smem, const float* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem));
+}
+
+// Lane `part` of a column holds rows part*NI .. part*NI + NI - 1.  In shared memory a k or q row keeps the four parts
+// NI + 4 floats apart, so that the four 16-byte reads a warp makes at a time fall on different banks.
+template <int NI>
+struct DeltaSmem {
+    static constexpr int ROW = 4 * (NI + 4);
+    float k[DR_CHUNK][ROW];
+    float q[DR_CHUNK][ROW];
+    float v[DR_CHUNK][DR_COLS];
+    float g[DR_CHUNK], beta[DR_CHUNK], kq[DR_CHUNK];      // g and beta arrive as logits and are turned in place
+};
+
 template <int NI>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(DeltaArgs a) {
-    constexpr int DP = NI * 4;                      // rows of S a column's four lanes cover
-    __shared__ float ks[DR_CHUNK][DP];
-    __shared__ float qs[DR_CHUNK][DP];
-    __shared__ float vs[DR_CHUNK][DR_COLS];
-    __shared__ float gs[DR_CHUNK], bs[DR_CHUNK];
+    static_assert(NI % 4 == 0, "rows per lane come in fours");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    DeltaSmem<NI>* bufs = reinterpret_cast<DeltaSmem<NI>*>(smem_raw);
 
     const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * DR_COLS;
     const int kv_head = head / (a.H / a.G);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int part = lane >> 3;                     // which rows: part, part + 4, ...
-    const int col = col0 + warp * 8 + (lane & 7);
+    const int part = lane >> 3;
+    const int col_in_block = warp * 8 + (lane & 7);
+    const int col = col0 + col_in_block;
     const bool col_ok = col < a.vdim;
     const int first = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - first;
     float* S_glob = a.state + (long long)a.slots[seq] * a.state_stride + (long long)head * a.dim * a.vdim;
@@ -141,85 +158,130 @@ delta_rule_kernel(DeltaArgs a) {
     float S[NI];
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
-        const int i = part + 4 * ii;
+        const int i = part * NI + ii;
         S[ii] = (col_ok && i < a.dim) ? S_glob[(long long)i * a.vdim + col] : 0.0f;
     }
     const float neg_rate = -expf(a.A_log[head]);
     const float dt_bias = a.dt_bias[head];
 
-    for (int t0 = 0; t0 < q_len; t0 += DR_CHUNK) {
+    // what a chunk brings: rows of q and k (zeros where dim ends), the block's columns of v, the two gate logits
+    auto fetch = [&](int t0, DeltaSmem<NI>& b) {
         const int n_t = min(DR_CHUNK, q_len - t0);
-        __syncthreads();                            // the chunk before has been read
-        for (int idx = tid; idx < DR_CHUNK * DP; idx += 128) {
-            const int t = idx / DP, i = idx % DP;
-            float kv = 0.0f, qv = 0.0f;
+        for (int idx = tid; idx < DR_CHUNK * 4 * NI; idx += 128) {
+            const int t = idx / (4 * NI), i = idx % (4 * NI);
+            const int at = i + 4 * (i / NI);
             if (t < n_t && i < a.dim) {
-                const float* row = a.qkv + (long long)(first + t0 + t) * a.qkv_stride;
-                kv = row[a.k_col + kv_head * a.dim + i];
-                qv = row[a.q_col + kv_head * a.dim + i];
+                const float* row = a.qkv + (long long)(first + t0 + t) * a.qkv_stride + kv_head * a.dim + i;
+                cp_async_f32(&b.k[t][at], row + a.k_col);
+                cp_async_f32(&b.q[t][at], row + a.q_col);
+            } else {
+                b.k[t][at] = 0.0f;
+                b.q[t][at] = 0.0f;
             }
-            ks[t][i] = kv;
-            qs[t][i] = qv;
         }
         for (int idx = tid; idx < DR_CHUNK * DR_COLS; idx += 128) {
             const int t = idx / DR_COLS, j = idx % DR_COLS;
-            float v = 0.0f;
             if (t < n_t && col0 + j < a.vdim)
-                v = a.qkv[(long long)(first + t0 + t) * a.qkv_stride + a.v_col + head * a.vdim + col0 + j];
-            vs[t][j] = v;
+                cp_async_f32(&b.v[t][j], a.qkv + (long long)(first + t0 + t) * a.qkv_stride + a.v_col + head * a.vdim + col0 + j);
+            else
+                b.v[t][j] = 0.0f;
         }
-        if (tid < DR_CHUNK) {
-            float g = 1.0f, b = 0.0f;
-            if (tid < n_t) {
-                const float* row = a.gates + (long long)(first + t0 + tid) * a.gates_stride;
-                g = expf(neg_rate * softplus_f(row[a.a_col + head] + dt_bias));
-                b = sigmoid_f(row[a.b_col + head]);
-            }
-            gs[tid] = g;
-            bs[tid] = b;
+        if (tid < 2 * DR_CHUNK) {
+            const int t = tid >> 1;
+            float* dst = (tid & 1) ? &b.beta[t] : &b.g[t];
+            if (t < n_t)
+                cp_async_f32(dst, a.gates + (long long)(first + t0 + t) * a.gates_stride + ((tid & 1) ? a.b_col : a.a_col) + head);
+            else
+                *dst = 0.0f;
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    fetch(0, bufs[0]);
+    int cur = 0;
+    for (int t0 = 0; t0 < q_len; t0 += DR_CHUNK, cur ^= 1) {
+        const int n_t = min(DR_CHUNK, q_len - t0);
+        DeltaSmem<NI>& b = bufs[cur];
+        if (t0 + DR_CHUNK < q_len) {
+            fetch(t0 + DR_CHUNK, bufs[cur ^ 1]);               // the other buffer's steps ended before the barrier below, last turn
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
-        // unit vectors: a warp per token
+        // prepare the chunk in place: unit vectors and k·q (a warp per token), decay and step size
         for (int t = warp; t < n_t; t += 4) {
-            float sk = 0.0f, sq = 0.0f;
-            for (int i = lane; i < a.dim; i += 32) {
-                sk += ks[t][i] * ks[t][i];
-                sq += qs[t][i] * qs[t][i];
+            float sk = 0.0f, sq = 0.0f, skq = 0.0f;
+            for (int i = lane; i < DeltaSmem<NI>::ROW; i += 32) {
+                const float kv = b.k[t][i], qv = b.q[t][i];    // the padding between the parts is never written: skip it
+                const bool real = (i % (NI + 4)) < NI;
+                sk += real ? kv * kv : 0.0f;
+                sq += real ? qv * qv : 0.0f;
+                skq += real ? kv * qv : 0.0f;
             }
             sk = warp_sum(sk);
             sq = warp_sum(sq);
+            skq = warp_sum(skq);
             const float fk = 1.0f / sqrtf(sk + 1e-6f), fq = a.q_scale / sqrtf(sq + 1e-6f);
-            for (int i = lane; i < a.dim; i += 32) {
-                ks[t][i] *= fk;
-                qs[t][i] *= fq;
+            for (int i = lane; i < DeltaSmem<NI>::ROW; i += 32) {
+                if ((i % (NI + 4)) < NI) {
+                    b.k[t][i] *= fk;
+                    b.q[t][i] *= fq;
+                }
+            }
+            if (lane == 0) {
+                b.kq[t] = skq * fk * fq;
+                b.g[t] = expf(neg_rate * softplus_f(b.g[t] + dt_bias));
+                b.beta[t] = sigmoid_f(b.beta[t]);
             }
         }
         __syncthreads();
         for (int t = 0; t < n_t; ++t) {
-            const float g = gs[t], beta = bs[t];
-            float dk = 0.0f;
+            const float4* k4 = reinterpret_cast<const float4*>(&b.k[t][part * (NI + 4)]);
+            const float4* q4 = reinterpret_cast<const float4*>(&b.q[t][part * (NI + 4)]);
+            float kr[NI];
+            float dk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int ii = 0; ii < NI; ++ii) dk = fmaf(S[ii], ks[t][part + 4 * ii], dk);
-            dk += __shfl_xor_sync(0xffffffffu, dk, 8);
-            dk += __shfl_xor_sync(0xffffffffu, dk, 16);
-            const float u = beta * (vs[t][warp * 8 + (lane & 7)] - g * dk);
-            float dq = 0.0f;
-#pragma unroll
-            for (int ii = 0; ii < NI; ++ii) {
-                S[ii] = fmaf(ks[t][part + 4 * ii], u, g * S[ii]);
-                dq = fmaf(S[ii], qs[t][part + 4 * ii], dq);
+            for (int v = 0; v < NI / 4; ++v) {
+                const float4 kk = k4[v], qq = q4[v];
+                kr[4 * v] = kk.x; kr[4 * v + 1] = kk.y; kr[4 * v + 2] = kk.z; kr[4 * v + 3] = kk.w;
+                dk[0] = fmaf(S[4 * v], kk.x, dk[0]);     dq[0] = fmaf(S[4 * v], qq.x, dq[0]);
+                dk[1] = fmaf(S[4 * v + 1], kk.y, dk[1]); dq[1] = fmaf(S[4 * v + 1], qq.y, dq[1]);
+                dk[2] = fmaf(S[4 * v + 2], kk.z, dk[2]); dq[2] = fmaf(S[4 * v + 2], qq.z, dq[2]);
+                dk[3] = fmaf(S[4 * v + 3], kk.w, dk[3]); dq[3] = fmaf(S[4 * v + 3], qq.w, dq[3]);
             }
-            dq += __shfl_xor_sync(0xffffffffu, dq, 8);
-            dq += __shfl_xor_sync(0xffffffffu, dq, 16);
+            float sk = (dk[0] + dk[1]) + (dk[2] + dk[3]), sq = (dq[0] + dq[1]) + (dq[2] + dq[3]);
+            sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+            sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+            const float g = b.g[t];
+            const float u = b.beta[t] * (b.v[t][col_in_block] - g * sk);
             if (part == 0 && col_ok)
-                a.out[(long long)(first + t0 + t) * a.H * a.vdim + (long long)head * a.vdim + col] = dq;
+                a.out[(long long)(first + t0 + t) * a.H * a.vdim + (long long)head * a.vdim + col] = fmaf(b.kq[t], u, g * sq);
+#pragma unroll
+            for (int ii = 0; ii < NI; ++ii) S[ii] = fmaf(kr[ii], u, g * S[ii]);
         }
+        __syncthreads();                                       // this buffer may be written again from the next turn on
     }
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
-        const int i = part + 4 * ii;
+        const int i = part * NI + ii;
         if (col_ok && i < a.dim) S_glob[(long long)i * a.vdim + col] = S[ii];
     }
+}
+
+template <int NI>
+static cudaError_t launch_delta_rule(const DeltaArgs& a, dim3 grid, cudaStream_t s) {
+    const size_t smem = 2 * sizeof(DeltaSmem<NI>);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        raised = true;
+    }
+    delta_rule_kernel<NI><<<grid, 128, smem, s>>>(a);
+    return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------ gated RMS norm of each head's output
@@ -366,6 +428,78 @@ __global__ void linear_scan_kernel(const float* __restrict__ av, const float* __
     *st = S;
 }
 
+// The same for long runs of tokens: 32 channels (a lane each) and SC_WARPS warps per block, the sequence's new tokens
+// cut into SC_WARPS consecutive segments.  A warp first folds its segment into the pair (A, D) with
+// S_end = A·S_begin + D; the pairs of the segments before it, applied in order to the sequence's state, give the
+// state its segment starts from; then it walks its segment token by token as above.  Eight tokens' loads are issued
+// together in both passes.
+constexpr int SC_WARPS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(SC_WARPS * 32)
+linear_scan_long_kernel(const float* __restrict__ av, const float* __restrict__ drive, const float* __restrict__ y,
+                        long long y_stride, const float* __restrict__ y_bias, float* state, long long state_stride,
+                        const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int W, float out_scale,
+                        T* __restrict__ out) {
+    __shared__ float As[SC_WARPS][32], Ds[SC_WARPS][32];
+    const int seq = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
+    const bool ok = c < W;
+    const int first = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - first;
+    const int per = (q_len + SC_WARPS - 1) / SC_WARPS;
+    const int lo = first + min(q_len, warp * per), hi = first + min(q_len, (warp + 1) * per);
+    float A = 1.0f, D = 0.0f;
+    if (ok && warp + 1 < SC_WARPS) {
+        int t = lo;
+        for (; t + 8 <= hi; t += 8) {
+            float a8[8], d8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                a8[e] = av[(long long)(t + e) * W + c];
+                d8[e] = drive[(long long)(t + e) * W + c];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                A *= a8[e];
+                D = fmaf(a8[e], D, d8[e]);
+            }
+        }
+        for (; t < hi; ++t) {
+            const float at = av[(long long)t * W + c];
+            A *= at;
+            D = fmaf(at, D, drive[(long long)t * W + c]);
+        }
+    }
+    As[warp][lane] = A;
+    Ds[warp][lane] = D;
+    __syncthreads();
+    if (!ok) return;
+    float* st = state + (long long)slots[seq] * state_stride + c;
+    float S = *st;
+    for (int u = 0; u < warp; ++u) S = fmaf(As[u][lane], S, Ds[u][lane]);
+    const float yb = y_bias != nullptr ? y_bias[c] : 0.0f;
+    int t = lo;
+    for (; t + 8 <= hi; t += 8) {
+        float a8[8], d8[8], y8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            a8[e] = av[(long long)(t + e) * W + c];
+            d8[e] = drive[(long long)(t + e) * W + c];
+            y8[e] = y[(long long)(t + e) * y_stride + c];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            S = fmaf(a8[e], S, d8[e]);
+            out[(long long)(t + e) * W + c] = from_float<T>(S * gelu_tanh_f(y8[e] + yb) * out_scale);
+        }
+    }
+    for (; t < hi; ++t) {
+        S = fmaf(av[(long long)t * W + c], S, drive[(long long)t * W + c]);
+        out[(long long)t * W + c] = from_float<T>(S * gelu_tanh_f(y[(long long)t * y_stride + c] + yb) * out_scale);
+    }
+    if (warp == SC_WARPS - 1) *st = S;
+}
+
 }  // namespace mlc
 
 using namespace mlc;
@@ -386,7 +520,8 @@ extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* 
         MLC_LAUNCH_CHECK();
         return 0;
     }
-    conv_out_kernel<<<(unsigned)(((long long)n_tokens * C + 255) / 256), 256, 0, s>>>(a);
+    if ((C + 255) / 256 > 65535) return MLC_ERR_BAD_SIZE;
+    conv_out_kernel<<<dim3(n_tokens, (C + 255) / 256), 256, 0, s>>>(a);
     MLC_LAUNCH_CHECK();
     if (taps > 1) {
         conv_state_kernel<<<(unsigned)(((long long)n_seqs * C + 255) / 256), 256, 0, s>>>(a);
@@ -406,15 +541,17 @@ extern "C" int mlc_gated_delta_rule(const float* qkv, long long qkv_stride, int 
     const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     const int ni = (dim + 3) / 4;
-    if (ni <= 8) delta_rule_kernel<8><<<grid, 128, 0, s>>>(a);
-    else if (ni <= 16) delta_rule_kernel<16><<<grid, 128, 0, s>>>(a);
-    else if (ni <= 24) delta_rule_kernel<24><<<grid, 128, 0, s>>>(a);
-    else if (ni <= 32) delta_rule_kernel<32><<<grid, 128, 0, s>>>(a);
-    else if (ni <= 48) delta_rule_kernel<48><<<grid, 128, 0, s>>>(a);
-    else delta_rule_kernel<64><<<grid, 128, 0, s>>>(a);
-    MLC_LAUNCH_CHECK();
+    cudaError_t e;
+    if (ni <= 8) e = launch_delta_rule<8>(a, grid, s);
+    else if (ni <= 16) e = launch_delta_rule<16>(a, grid, s);
+    else if (ni <= 24) e = launch_delta_rule<24>(a, grid, s);
+    else if (ni <= 32) e = launch_delta_rule<32>(a, grid, s);
+    else if (ni <= 48) e = launch_delta_rule<48>(a, grid, s);
+    else e = launch_delta_rule<64>(a, grid, s);
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
+
 
 extern "C" int mlc_gated_rmsnorm(const float* o, const float* gate, long long gate_stride, const float* w, float eps,
                                  long long n_tokens, int H, int vdim, void* out, int out_dtype, void* stream) {
@@ -448,11 +585,22 @@ extern "C" int mlc_block_gates(const float* u, const float* wr, const float* wi,
 
 extern "C" int mlc_linear_scan(const float* av, const float* drive, const float* y, long long y_stride, const float* y_bias,
                                float* state, long long state_stride, const int* slots, const int* cu_seqlens, int n_seqs, int W,
-                               float out_scale, void* out, int out_dtype, void* stream) {
+                               int max_q_len, float out_scale, void* out, int out_dtype, void* stream) {
     if (n_seqs <= 0) return 0;
     if (W <= 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
-    const dim3 grid((W + 127) / 128, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
+    if (max_q_len >= 4 * SC_WARPS) {                      // long runs of tokens: segments scanned side by side
+        const dim3 grid((W + 31) / 32, n_seqs);
+        if (out_dtype == MLC_DTYPE_F32)
+            linear_scan_long_kernel<float><<<grid, SC_WARPS * 32, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (float*)out);
+        else if (out_dtype == MLC_DTYPE_BF16)
+            linear_scan_long_kernel<bf16><<<grid, SC_WARPS * 32, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (bf16*)out);
+        else
+            return MLC_ERR_BAD_DTYPE;
+        MLC_LAUNCH_CHECK();
+        return 0;
+    }
+    const dim3 grid((W + 127) / 128, n_seqs);
     if (out_dtype == MLC_DTYPE_F32)
         linear_scan_kernel<float><<<grid, 128, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (float*)out);
     else if (out_dtype == MLC_DTYPE_BF16)

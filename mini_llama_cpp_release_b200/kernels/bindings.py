@@ -97,7 +97,7 @@ def core() -> ctypes.CDLL:
             "mlc_gated_delta_rule": [P, LL, I, I, I, P, LL, I, I, P, P, P, LL, P, P, I, I, I, I, I, P, P],
             "mlc_gated_rmsnorm": [P, P, LL, P, F, LL, I, I, P, I, P],
             "mlc_block_gates": [P, P, P, P, P, P, I, I, I, F, P, P, P],
-            "mlc_linear_scan": [P, P, P, LL, P, P, LL, P, P, I, I, F, P, I, P],
+            "mlc_linear_scan": [P, P, P, LL, P, P, LL, P, P, I, I, I, F, P, I, P],
             "mlc_qkv_post": [P, P, P, P, P, I, I, I, I, I, P, I, P, P, P, LL, I, I, I, P],
             "mlc_silu_mul": [P, I, I, I, I, P, I, P],
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
@@ -486,7 +486,8 @@ def linear_scan(a: torch.Tensor, drive: torch.Tensor, y: torch.Tensor, y_col: in
     assert a.dtype == drive.dtype == torch.float32 and out.shape == (n, W) and state.shape[1] == W
     _check(core().mlc_linear_scan(a.data_ptr(), drive.data_ptr(), _columns(y, y_col), y.stride(0), _ptr(y_bias),
                                   state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(),
-                                  step.n_seqs, W, float(out_scale), out.data_ptr(), dtype_code(out.dtype), _stream()),
+                                  step.n_seqs, W, step.max_q_len, float(out_scale), out.data_ptr(), dtype_code(out.dtype),
+                                  _stream()),
            "linear recurrence")
 
 

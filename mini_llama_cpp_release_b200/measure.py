@@ -24,6 +24,22 @@ from typing import Any, Dict, List, Optional, Sequence
 
 _QWEN2 = dict(architectures=["Qwen2ForCausalLM"], hidden_act="silu", attention_bias=True, use_sliding_window=False)
 
+def _mepolix(width: int, ff: int, heads: int, kv_heads: int, head: int, n_layers: int, vocab: int, every: int = 3) -> Dict[str, Any]:
+    """Mepolix layers of real width: two delta-rule layers, then one with attention beside a recurrence, and so on; the
+    attention's shape (heads, kv heads, head size), the feed-forward and the width are the Qwen2 preset's of the same
+    width, so that the two can be timed side by side.  Every layer has the feed-forward."""
+    delta = {"type": "delta", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": head, "vdim": head, "conv": 4}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                              "rot": {"dims": head // 2, "base": 500000.0,
+                                      "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+                     "right": {"width": width, "blocks": max(1, width // 128), "conv": 4},
+                     "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Mepolix", "vocab": vocab, "width": width, "logit_softcap": 30.0, "norm": {"eps": 1e-6},
+            "layers": [dict(par) if i % every == every - 1 else dict(delta) for i in range(n_layers)]}
+
+
 PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-a": dict(_QWEN2, hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
                    num_key_value_heads=2, head_dim=16, vocab_size=512, max_position_embeddings=256, rope_theta=10000.0,
@@ -40,6 +56,10 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "qwen2-7b": dict(_QWEN2, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28,
                      num_key_value_heads=4, head_dim=128, vocab_size=152064, max_position_embeddings=32768,
                      rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False),
+    # the Mepolix design at the widths of the Qwen2 presets (see `_mepolix`)
+    "mepolix-w896": _mepolix(896, 4864, 14, 2, 64, 24, 151936),
+    "mepolix-w1536": _mepolix(1536, 8960, 12, 2, 128, 28, 151936),
+    "mepolix-w3584": _mepolix(3584, 18944, 28, 4, 128, 28, 152064),
 }
 
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
@@ -293,6 +313,30 @@ def prefill_flops(raw: Dict[str, Any], layers: int, lengths: Sequence[int]) -> f
     attention = layers * H * 2.0 * sum(float(n) * n for n in lengths) * hd
     head = 2.0 * V * d * len(lengths)
     return linear + attention + head
+
+
+def model_prefill_flops(model, lengths: Sequence[int]) -> float:
+    """The same count for any model, read off its parts: 2 x tokens x the elements of every matrix a run of the
+    schedule multiplies by, causal attention of every mixer that keeps keys (its head count and head size), and the
+    head at one position per sequence.  Recurrences and convolutions, linear in the tokens and small, are left out."""
+    from .parts.attention import GQAttention
+    from .parts.linear import Linear
+
+    def walk(part):
+        yield part
+        for c in part.children():
+            yield from walk(c)
+    T = float(sum(lengths))
+    squares = sum(float(n) * n for n in lengths)
+    total = 0.0
+    for entry in model.spec.schedule:
+        for part in walk(model.parts.blocks[entry.layer]):
+            for v in vars(part).values():
+                if isinstance(v, Linear):
+                    total += 2.0 * T * v.weight.numel()
+            if isinstance(part, GQAttention):
+                total += part.H * 2.0 * squares * part.hd
+    return total + 2.0 * model.config.vocab_size * model.parts.head.hidden * len(lengths)
 
 
 def roofline(step_bytes: float, ms_per_step: float, pk: Dict[str, Any]) -> Dict[str, Any]:
