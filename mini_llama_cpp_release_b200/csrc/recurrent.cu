@@ -42,21 +42,41 @@ struct ConvArgs {
 
 __device__ __forceinline__ float conv_finish(float acc, int act) { return act == 1 ? acc * sigmoid_f(acc) : acc; }
 
-__global__ void conv_out_kernel(ConvArgs a) {
-    const int token = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c >= a.C) return;
-    const int seq = a.tok_seq[token];
-    const int t = token - a.cu_seqlens[seq];
-    const float* st = a.state + (long long)a.slots[seq] * a.state_stride;
-    const float* w = a.w + (long long)c * a.taps;
-    float acc = a.bias != nullptr ? a.bias[c] : 0.0f;
-    const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
-    for (int j = 0; j < a.taps; ++j) {
-        const int src = t - j;
-        const float v = src >= 0 ? a.x[(long long)(token - j) * a.x_stride + c] + ib : st[(long long)(a.taps - 1 + src) * a.C + c];
-        acc = fmaf(w[a.taps - 1 - j], v, acc);
+// A block takes CONV_TOKENS consecutive tokens x 256 channels: where each token stands in its sequence is looked up once
+// per block, after which every load of the tile is independent of every other.
+constexpr int CONV_TOKENS = 16;
+
+__global__ void __launch_bounds__(256)
+conv_out_kernel(ConvArgs a) {
+    __shared__ int t_of[CONV_TOKENS];
+    __shared__ long long state_of[CONV_TOKENS];
+    const int tok0 = blockIdx.x * CONV_TOKENS, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (threadIdx.x < CONV_TOKENS) {
+        const int token = tok0 + threadIdx.x;
+        if (token < a.n_tokens) {
+            const int seq = a.tok_seq[token];
+            t_of[threadIdx.x] = token - a.cu_seqlens[seq];
+            state_of[threadIdx.x] = (long long)a.slots[seq] * a.state_stride;
+        }
     }
-    a.out[(long long)token * a.out_stride + c] = conv_finish(acc, a.act);
+    __syncthreads();
+    if (c >= a.C) return;
+    const float* w = a.w + (long long)c * a.taps;
+    const float b0 = a.bias != nullptr ? a.bias[c] : 0.0f;
+    const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
+    const int n_here = min(CONV_TOKENS, a.n_tokens - tok0);
+#pragma unroll 4
+    for (int i = 0; i < n_here; ++i) {
+        const int token = tok0 + i, t = t_of[i];
+        const float* st = a.state + state_of[i];
+        float acc = b0;
+        for (int j = 0; j < a.taps; ++j) {
+            const int src = t - j;
+            const float v = src >= 0 ? a.x[(long long)(token - j) * a.x_stride + c] + ib : st[(long long)(a.taps - 1 + src) * a.C + c];
+            acc = fmaf(w[a.taps - 1 - j], v, acc);
+        }
+        a.out[(long long)token * a.out_stride + c] = conv_finish(acc, a.act);
+    }
 }
 
 // After conv_out_kernel: the state becomes the last taps-1 inputs of the lengthened sequence.
@@ -94,15 +114,18 @@ __global__ void conv_step_kernel(ConvArgs a) {
 // Per head, with a state S [dim][vdim] and, for a token, unit vectors k and q (q also times dim^-1/2), a value row v,
 // a decay g in (0, 1) and a step size beta in (0, 1):
 //     S <- g·S;   u = beta·(v - Sᵀk);   S <- S + k uᵀ;   o = Sᵀq.
-// The columns of S never meet, so a block owns 32 of them for one (sequence, head) and walks the sequence's tokens in
-// order; a column is shared by 4 lanes, each holding a quarter of its rows in registers.  With the state before the
-// token, S', the token needs two dot products per column that do not wait for each other, and the read-out follows
-// from them:  dk = S'ᵀk,  dq = S'ᵀq,  u = beta·(v - g·dk),  o = g·dq + (k·q)·u,  S = g·S' + k uᵀ.
+// Two kernels.  The first is parallel over tokens: per (token, head) the five numbers the recurrence needs beside the
+// raw rows: g, beta, the factors fk = 1/sqrt(|k|² + 1e-6) and fq = dim^-1/2 / sqrt(|q|² + 1e-6) that make k and q unit
+// vectors, and k·q of the unit vectors.  The second walks each sequence's tokens in order.  The columns of S never
+// meet, so a block owns 32 of them for one (sequence, head); a warp owns 8, a lane two neighbouring columns and an
+// eighth of their rows, in registers.  With the state before the token, S', and the raw rows k', q':
+//     dk = fk·S'ᵀk',  dq = fq·S'ᵀq'   (two dot products per column that do not wait for each other)
+//     u = beta·(v - g·dk),  o = g·dq + (k·q)·u,  S = g·S' + k' (fk·u)ᵀ.
 // Tokens come in chunks of DR_CHUNK through two shared-memory buffers: while one chunk's steps run, the next
-// chunk's q, k, v rows and gate logits are on their way (cp.async); a chunk that has arrived is prepared in place
-// (unit vectors, k·q, decays, step sizes) and then its steps touch global memory for the outputs only.
+// chunk's rows and numbers are on their way (cp.async), and the steps touch global memory for the outputs only.
 constexpr int DR_CHUNK = 16;
 constexpr int DR_COLS = 32;
+constexpr int DR_COEF = 5;      // g, beta, fk, fq, k·q
 
 struct DeltaArgs {
     const float* qkv;           // rows of qkv_stride floats: q heads at q_col, k heads at k_col (G x dim each), v at v_col (H x vdim)
@@ -113,29 +136,59 @@ struct DeltaArgs {
     int b_col, a_col;
     const float* A_log;         // [H]
     const float* dt_bias;       // [H]
+    float* coef;                // [n_tokens][H][DR_COEF], written by the first kernel
     float* state;               // slot s: state + s * state_stride, [H][dim][vdim]
     long long state_stride;
     const int* slots;
     const int* cu_seqlens;
     float* out;                 // [n_tokens][H * vdim]
-    int H, G, dim, vdim;
+    int H, G, dim, vdim, n_tokens;
     float q_scale;              // dim^-1/2
 };
+
+__global__ void delta_prepare_kernel(DeltaArgs a) {
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)a.n_tokens * a.H) return;
+    const int lane = threadIdx.x & 31;
+    const int token = (int)(w / a.H), head = (int)(w % a.H);
+    const int kv_head = head / (a.H / a.G);
+    const float* row = a.qkv + (long long)token * a.qkv_stride + kv_head * a.dim;
+    float sk = 0.0f, sq = 0.0f, skq = 0.0f;
+    for (int i = lane; i < a.dim; i += 32) {
+        const float kv = row[a.k_col + i], qv = row[a.q_col + i];
+        sk = fmaf(kv, kv, sk);
+        sq = fmaf(qv, qv, sq);
+        skq = fmaf(kv, qv, skq);
+    }
+    sk = warp_sum(sk);
+    sq = warp_sum(sq);
+    skq = warp_sum(skq);
+    if (lane == 0) {
+        const float* gr = a.gates + (long long)token * a.gates_stride;
+        const float fk = 1.0f / sqrtf(sk + 1e-6f), fq = a.q_scale / sqrtf(sq + 1e-6f);
+        float* c = a.coef + w * DR_COEF;
+        c[0] = expf(-expf(a.A_log[head]) * softplus_f(gr[a.a_col + head] + a.dt_bias[head]));
+        c[1] = sigmoid_f(gr[a.b_col + head]);
+        c[2] = fk;
+        c[3] = fq;
+        c[4] = skq * fk * fq;
+    }
+}
 
 __device__ __forceinline__ void cp_async_f32(float* smem, const float* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem));
 }
 
-// Lane `part` of a column holds rows part*NI .. part*NI + NI - 1.  In shared memory a k or q row keeps the four parts
-// NI + 4 floats apart, so that the four 16-byte reads a warp makes at a time fall on different banks.
+// Row part p of 8 holds rows p*NI .. p*NI + NI - 1.  In shared memory a k or q row keeps the parts NI + 4 floats apart, so
+// that the 16-byte reads a warp makes at a time fall on different banks.
 template <int NI>
 struct DeltaSmem {
-    static constexpr int ROW = 4 * (NI + 4);
+    static constexpr int ROW = 8 * (NI + 4);
     float k[DR_CHUNK][ROW];
     float q[DR_CHUNK][ROW];
     float v[DR_CHUNK][DR_COLS];
-    float g[DR_CHUNK], beta[DR_CHUNK], kq[DR_CHUNK];      // g and beta arrive as logits and are turned in place
+    float coef[DR_CHUNK][8];
 };
 
 template <int NI>
@@ -148,27 +201,26 @@ delta_rule_kernel(DeltaArgs a) {
     const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * DR_COLS;
     const int kv_head = head / (a.H / a.G);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int part = lane >> 3;
-    const int col_in_block = warp * 8 + (lane & 7);
+    const int part = lane >> 2;                               // 0..7: which rows
+    const int col_in_block = warp * 8 + (lane & 3) * 2;       // this lane's two columns
     const int col = col0 + col_in_block;
-    const bool col_ok = col < a.vdim;
+    const bool ok0 = col < a.vdim, ok1 = col + 1 < a.vdim;
     const int first = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - first;
     float* S_glob = a.state + (long long)a.slots[seq] * a.state_stride + (long long)head * a.dim * a.vdim;
 
-    float S[NI];
+    float S0[NI], S1[NI];
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
         const int i = part * NI + ii;
-        S[ii] = (col_ok && i < a.dim) ? S_glob[(long long)i * a.vdim + col] : 0.0f;
+        S0[ii] = (ok0 && i < a.dim) ? S_glob[(long long)i * a.vdim + col] : 0.0f;
+        S1[ii] = (ok1 && i < a.dim) ? S_glob[(long long)i * a.vdim + col + 1] : 0.0f;
     }
-    const float neg_rate = -expf(a.A_log[head]);
-    const float dt_bias = a.dt_bias[head];
 
-    // what a chunk brings: rows of q and k (zeros where dim ends), the block's columns of v, the two gate logits
+    // what a chunk brings: raw rows of q and k (zeros where dim ends), the block's columns of v, the tokens' five numbers
     auto fetch = [&](int t0, DeltaSmem<NI>& b) {
         const int n_t = min(DR_CHUNK, q_len - t0);
-        for (int idx = tid; idx < DR_CHUNK * 4 * NI; idx += 128) {
-            const int t = idx / (4 * NI), i = idx % (4 * NI);
+        for (int idx = tid; idx < DR_CHUNK * 8 * NI; idx += 128) {
+            const int t = idx / (8 * NI), i = idx % (8 * NI);
             const int at = i + 4 * (i / NI);
             if (t < n_t && i < a.dim) {
                 const float* row = a.qkv + (long long)(first + t0 + t) * a.qkv_stride + kv_head * a.dim + i;
@@ -186,13 +238,9 @@ delta_rule_kernel(DeltaArgs a) {
             else
                 b.v[t][j] = 0.0f;
         }
-        if (tid < 2 * DR_CHUNK) {
-            const int t = tid >> 1;
-            float* dst = (tid & 1) ? &b.beta[t] : &b.g[t];
-            if (t < n_t)
-                cp_async_f32(dst, a.gates + (long long)(first + t0 + t) * a.gates_stride + ((tid & 1) ? a.b_col : a.a_col) + head);
-            else
-                *dst = 0.0f;
+        if (tid < DR_CHUNK * DR_COEF) {
+            const int t = tid / DR_COEF, e = tid % DR_COEF;
+            if (t < n_t) cp_async_f32(&b.coef[t][e], a.coef + ((long long)(first + t0 + t) * a.H + head) * DR_COEF + e);
         }
         asm volatile("cp.async.commit_group;\n" ::);
     };
@@ -209,65 +257,56 @@ delta_rule_kernel(DeltaArgs a) {
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
-        // prepare the chunk in place: unit vectors and k·q (a warp per token), decay and step size
-        for (int t = warp; t < n_t; t += 4) {
-            float sk = 0.0f, sq = 0.0f, skq = 0.0f;
-            for (int i = lane; i < DeltaSmem<NI>::ROW; i += 32) {
-                const float kv = b.k[t][i], qv = b.q[t][i];    // the padding between the parts is never written: skip it
-                const bool real = (i % (NI + 4)) < NI;
-                sk += real ? kv * kv : 0.0f;
-                sq += real ? qv * qv : 0.0f;
-                skq += real ? kv * qv : 0.0f;
-            }
-            sk = warp_sum(sk);
-            sq = warp_sum(sq);
-            skq = warp_sum(skq);
-            const float fk = 1.0f / sqrtf(sk + 1e-6f), fq = a.q_scale / sqrtf(sq + 1e-6f);
-            for (int i = lane; i < DeltaSmem<NI>::ROW; i += 32) {
-                if ((i % (NI + 4)) < NI) {
-                    b.k[t][i] *= fk;
-                    b.q[t][i] *= fq;
-                }
-            }
-            if (lane == 0) {
-                b.kq[t] = skq * fk * fq;
-                b.g[t] = expf(neg_rate * softplus_f(b.g[t] + dt_bias));
-                b.beta[t] = sigmoid_f(b.beta[t]);
-            }
-        }
-        __syncthreads();
         for (int t = 0; t < n_t; ++t) {
             const float4* k4 = reinterpret_cast<const float4*>(&b.k[t][part * (NI + 4)]);
             const float4* q4 = reinterpret_cast<const float4*>(&b.q[t][part * (NI + 4)]);
+            const float4 c03 = *reinterpret_cast<const float4*>(&b.coef[t][0]);      // g, beta, fk, fq
+            const float kq = b.coef[t][4];
+            const float2 vv = *reinterpret_cast<const float2*>(&b.v[t][col_in_block]);
             float kr[NI];
-            float dk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float dk0[2] = {0.0f, 0.0f}, dk1[2] = {0.0f, 0.0f}, dq0[2] = {0.0f, 0.0f}, dq1[2] = {0.0f, 0.0f};
 #pragma unroll
             for (int v = 0; v < NI / 4; ++v) {
                 const float4 kk = k4[v], qq = q4[v];
                 kr[4 * v] = kk.x; kr[4 * v + 1] = kk.y; kr[4 * v + 2] = kk.z; kr[4 * v + 3] = kk.w;
-                dk[0] = fmaf(S[4 * v], kk.x, dk[0]);     dq[0] = fmaf(S[4 * v], qq.x, dq[0]);
-                dk[1] = fmaf(S[4 * v + 1], kk.y, dk[1]); dq[1] = fmaf(S[4 * v + 1], qq.y, dq[1]);
-                dk[2] = fmaf(S[4 * v + 2], kk.z, dk[2]); dq[2] = fmaf(S[4 * v + 2], qq.z, dq[2]);
-                dk[3] = fmaf(S[4 * v + 3], kk.w, dk[3]); dq[3] = fmaf(S[4 * v + 3], qq.w, dq[3]);
+                dk0[0] = fmaf(S0[4 * v], kk.x, dk0[0]);     dk1[0] = fmaf(S1[4 * v], kk.x, dk1[0]);
+                dq0[0] = fmaf(S0[4 * v], qq.x, dq0[0]);     dq1[0] = fmaf(S1[4 * v], qq.x, dq1[0]);
+                dk0[1] = fmaf(S0[4 * v + 1], kk.y, dk0[1]); dk1[1] = fmaf(S1[4 * v + 1], kk.y, dk1[1]);
+                dq0[1] = fmaf(S0[4 * v + 1], qq.y, dq0[1]); dq1[1] = fmaf(S1[4 * v + 1], qq.y, dq1[1]);
+                dk0[0] = fmaf(S0[4 * v + 2], kk.z, dk0[0]); dk1[0] = fmaf(S1[4 * v + 2], kk.z, dk1[0]);
+                dq0[0] = fmaf(S0[4 * v + 2], qq.z, dq0[0]); dq1[0] = fmaf(S1[4 * v + 2], qq.z, dq1[0]);
+                dk0[1] = fmaf(S0[4 * v + 3], kk.w, dk0[1]); dk1[1] = fmaf(S1[4 * v + 3], kk.w, dk1[1]);
+                dq0[1] = fmaf(S0[4 * v + 3], qq.w, dq0[1]); dq1[1] = fmaf(S1[4 * v + 3], qq.w, dq1[1]);
             }
-            float sk = (dk[0] + dk[1]) + (dk[2] + dk[3]), sq = (dq[0] + dq[1]) + (dq[2] + dq[3]);
-            sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-            sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-            sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-            const float g = b.g[t];
-            const float u = b.beta[t] * (b.v[t][col_in_block] - g * sk);
-            if (part == 0 && col_ok)
-                a.out[(long long)(first + t0 + t) * a.H * a.vdim + (long long)head * a.vdim + col] = fmaf(b.kq[t], u, g * sq);
+            float sk0 = dk0[0] + dk0[1], sk1 = dk1[0] + dk1[1], sq0 = dq0[0] + dq0[1], sq1 = dq1[0] + dq1[1];
 #pragma unroll
-            for (int ii = 0; ii < NI; ++ii) S[ii] = fmaf(kr[ii], u, g * S[ii]);
+            for (int o = 4; o <= 16; o <<= 1) {
+                sk0 += __shfl_xor_sync(0xffffffffu, sk0, o);
+                sk1 += __shfl_xor_sync(0xffffffffu, sk1, o);
+                sq0 += __shfl_xor_sync(0xffffffffu, sq0, o);
+                sq1 += __shfl_xor_sync(0xffffffffu, sq1, o);
+            }
+            const float g = c03.x, beta = c03.y, fk = c03.z, fq = c03.w;
+            const float u0 = beta * (vv.x - g * (fk * sk0)), u1 = beta * (vv.y - g * (fk * sk1));
+            if (part == 0) {
+                float* o = a.out + (long long)(first + t0 + t) * a.H * a.vdim + (long long)head * a.vdim + col;
+                if (ok0) o[0] = fmaf(kq, u0, g * (fq * sq0));
+                if (ok1) o[1] = fmaf(kq, u1, g * (fq * sq1));
+            }
+            const float w0 = fk * u0, w1 = fk * u1;
+#pragma unroll
+            for (int ii = 0; ii < NI; ++ii) {
+                S0[ii] = fmaf(kr[ii], w0, g * S0[ii]);
+                S1[ii] = fmaf(kr[ii], w1, g * S1[ii]);
+            }
         }
         __syncthreads();                                       // this buffer may be written again from the next turn on
     }
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
         const int i = part * NI + ii;
-        if (col_ok && i < a.dim) S_glob[(long long)i * a.vdim + col] = S[ii];
+        if (ok0 && i < a.dim) S_glob[(long long)i * a.vdim + col] = S0[ii];
+        if (ok1 && i < a.dim) S_glob[(long long)i * a.vdim + col + 1] = S1[ii];
     }
 }
 
@@ -521,7 +560,7 @@ extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* 
         return 0;
     }
     if ((C + 255) / 256 > 65535) return MLC_ERR_BAD_SIZE;
-    conv_out_kernel<<<dim3(n_tokens, (C + 255) / 256), 256, 0, s>>>(a);
+    conv_out_kernel<<<dim3((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + 255) / 256), 256, 0, s>>>(a);
     MLC_LAUNCH_CHECK();
     if (taps > 1) {
         conv_state_kernel<<<(unsigned)(((long long)n_seqs * C + 255) / 256), 256, 0, s>>>(a);
@@ -530,28 +569,30 @@ extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* 
     return 0;
 }
 
+// coef: scratch of n_tokens * H * 5 floats.
 extern "C" int mlc_gated_delta_rule(const float* qkv, long long qkv_stride, int q_col, int k_col, int v_col, const float* gates,
                                     long long gates_stride, int b_col, int a_col, const float* A_log, const float* dt_bias,
-                                    float* state, long long state_stride, const int* slots, const int* cu_seqlens, int n_seqs,
-                                    int H, int G, int dim, int vdim, float* out, void* stream) {
-    if (n_seqs <= 0) return 0;
+                                    float* coef, float* state, long long state_stride, const int* slots, const int* cu_seqlens,
+                                    int n_seqs, int n_tokens, int H, int G, int dim, int vdim, float* out, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535 || H > 65535) return MLC_ERR_BAD_SIZE;
-    DeltaArgs a{qkv, qkv_stride, q_col, k_col, v_col, gates, gates_stride, b_col, a_col, A_log, dt_bias, state, state_stride,
-                slots, cu_seqlens, out, H, G, dim, vdim, 1.0f / sqrtf((float)dim)};
-    const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs);
+    DeltaArgs a{qkv, qkv_stride, q_col, k_col, v_col, gates, gates_stride, b_col, a_col, A_log, dt_bias, coef, state, state_stride,
+                slots, cu_seqlens, out, H, G, dim, vdim, n_tokens, 1.0f / sqrtf((float)dim)};
     cudaStream_t s = (cudaStream_t)stream;
-    const int ni = (dim + 3) / 4;
+    delta_prepare_kernel<<<(unsigned)(((long long)n_tokens * H + 7) / 8), 256, 0, s>>>(a);
+    MLC_LAUNCH_CHECK();
+    const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs);
+    const int ni = (dim + 7) / 8;
     cudaError_t e;
-    if (ni <= 8) e = launch_delta_rule<8>(a, grid, s);
+    if (ni <= 4) e = launch_delta_rule<4>(a, grid, s);
+    else if (ni <= 8) e = launch_delta_rule<8>(a, grid, s);
+    else if (ni <= 12) e = launch_delta_rule<12>(a, grid, s);
     else if (ni <= 16) e = launch_delta_rule<16>(a, grid, s);
     else if (ni <= 24) e = launch_delta_rule<24>(a, grid, s);
-    else if (ni <= 32) e = launch_delta_rule<32>(a, grid, s);
-    else if (ni <= 48) e = launch_delta_rule<48>(a, grid, s);
-    else e = launch_delta_rule<64>(a, grid, s);
+    else e = launch_delta_rule<32>(a, grid, s);
     if (e != cudaSuccess) return (int)e;
     return 0;
 }
-
 
 extern "C" int mlc_gated_rmsnorm(const float* o, const float* gate, long long gate_stride, const float* w, float eps,
                                  long long n_tokens, int H, int vdim, void* out, int out_dtype, void* stream) {
