@@ -42,14 +42,18 @@ struct ConvArgs {
 
 __device__ __forceinline__ float conv_finish(float acc, int act) { return act == 1 ? acc * sigmoid_f(acc) : acc; }
 
-// A block takes CONV_TOKENS consecutive tokens x 256 channels: where each token stands in its sequence is looked up once
-// per block, after which every load of the tile is independent of every other.
+// A block takes CONV_TOKENS consecutive tokens x 256 channels.  Where each token stands in its sequence is looked up
+// once per block; the tile's inputs, with the taps-1 rows before it, are loaded in one sweep of independent loads into
+// shared memory (a thread reads back only what it wrote itself); only a sequence's first taps-1 tokens reach for the
+// state.  CONV_MAX_TAPS bounds the rows kept; longer filters take the plain kernel below.
 constexpr int CONV_TOKENS = 16;
+constexpr int CONV_MAX_TAPS = 8;
 
 __global__ void __launch_bounds__(256)
 conv_out_kernel(ConvArgs a) {
     __shared__ int t_of[CONV_TOKENS];
     __shared__ long long state_of[CONV_TOKENS];
+    __shared__ float tile[CONV_TOKENS + CONV_MAX_TAPS - 1][256];
     const int tok0 = blockIdx.x * CONV_TOKENS, c = blockIdx.y * blockDim.x + threadIdx.x;
     if (threadIdx.x < CONV_TOKENS) {
         const int token = tok0 + threadIdx.x;
@@ -61,22 +65,56 @@ conv_out_kernel(ConvArgs a) {
     }
     __syncthreads();
     if (c >= a.C) return;
-    const float* w = a.w + (long long)c * a.taps;
-    const float b0 = a.bias != nullptr ? a.bias[c] : 0.0f;
+    const int halo = a.taps - 1;
     const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
     const int n_here = min(CONV_TOKENS, a.n_tokens - tok0);
-#pragma unroll 4
-    for (int i = 0; i < n_here; ++i) {
-        const int token = tok0 + i, t = t_of[i];
-        const float* st = a.state + state_of[i];
-        float acc = b0;
-        for (int j = 0; j < a.taps; ++j) {
-            const int src = t - j;
-            const float v = src >= 0 ? a.x[(long long)(token - j) * a.x_stride + c] + ib : st[(long long)(a.taps - 1 + src) * a.C + c];
-            acc = fmaf(w[a.taps - 1 - j], v, acc);
-        }
-        a.out[(long long)token * a.out_stride + c] = conv_finish(acc, a.act);
+    float in[CONV_TOKENS + CONV_MAX_TAPS - 1];
+#pragma unroll
+    for (int r = 0; r < CONV_TOKENS + CONV_MAX_TAPS - 1; ++r) {      // every load of the tile in flight at once
+        const int token = tok0 - halo + r;
+        in[r] = (r < n_here + halo && token >= 0) ? a.x[(long long)token * a.x_stride + c] : 0.0f;
     }
+#pragma unroll
+    for (int r = 0; r < CONV_TOKENS + CONV_MAX_TAPS - 1; ++r) tile[r][threadIdx.x] = in[r] + ib;
+    float w[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < a.taps ? a.w[(long long)c * a.taps + a.taps - 1 - j] : 0.0f;
+    const float b0 = a.bias != nullptr ? a.bias[c] : 0.0f;
+    for (int i = 0; i < n_here; ++i) {
+        const int t = t_of[i];
+        float acc = b0;
+        if (t >= halo) {
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; ++j)
+                if (j < a.taps) acc = fmaf(w[j], tile[i + halo - j][threadIdx.x], acc);
+        } else {
+            const float* st = a.state + state_of[i];
+            for (int j = 0; j < a.taps; ++j) {
+                const int src = t - j;
+                const float v = src >= 0 ? tile[i + halo - j][threadIdx.x] : st[(long long)(halo + src) * a.C + c];
+                acc = fmaf(a.w[(long long)c * a.taps + a.taps - 1 - j], v, acc);
+            }
+        }
+        a.out[(long long)(tok0 + i) * a.out_stride + c] = conv_finish(acc, a.act);
+    }
+}
+
+// Any number of taps: a thread per (token, channel).
+__global__ void conv_out_plain_kernel(ConvArgs a) {
+    const int token = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= a.C) return;
+    const int seq = a.tok_seq[token];
+    const int t = token - a.cu_seqlens[seq];
+    const float* st = a.state + (long long)a.slots[seq] * a.state_stride;
+    const float* w = a.w + (long long)c * a.taps;
+    float acc = a.bias != nullptr ? a.bias[c] : 0.0f;
+    const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
+    for (int j = 0; j < a.taps; ++j) {
+        const int src = t - j;
+        const float v = src >= 0 ? a.x[(long long)(token - j) * a.x_stride + c] + ib : st[(long long)(a.taps - 1 + src) * a.C + c];
+        acc = fmaf(w[a.taps - 1 - j], v, acc);
+    }
+    a.out[(long long)token * a.out_stride + c] = conv_finish(acc, a.act);
 }
 
 // After conv_out_kernel: the state becomes the last taps-1 inputs of the lengthened sequence.
@@ -539,6 +577,77 @@ linear_scan_long_kernel(const float* __restrict__ av, const float* __restrict__ 
     if (warp == SC_WARPS - 1) *st = S;
 }
 
+// One token per sequence (token b belongs to sequence b): gates and recurrence in one kernel.  A block takes 32 channels
+// of one gate block for up to GS_SEQS sequences; lane = channel, the eight warps share out the inner index and meet in
+// shared memory.  The gate matrices come transposed, [block][in][out], so that a warp reads 32 neighbouring outputs of
+// one input at a time.
+constexpr int GS_SEQS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gates_scan_step_kernel(const float* __restrict__ u, const float* __restrict__ wr_t, const float* __restrict__ wi_t,
+                       const float* __restrict__ br, const float* __restrict__ bi, const float* __restrict__ lam, float c,
+                       const float* __restrict__ y, long long y_stride, const float* __restrict__ y_bias, float* state,
+                       long long state_stride, const int* __restrict__ slots, int n_seqs, int W, int bw, float out_scale,
+                       T* __restrict__ out) {
+    extern __shared__ float gs_smem[];
+    float* us = gs_smem;                                  // [GS_SEQS][bw]
+    float* part = us + GS_SEQS * bw;                      // [8 warps][GS_SEQS][2][32]
+    const int chunks = (bw + 31) / 32;
+    const int blk = blockIdx.x / chunks, oc0 = (blockIdx.x % chunks) * 32;
+    const int seq0 = blockIdx.y * GS_SEQS, n_here = min(GS_SEQS, n_seqs - seq0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int idx = threadIdx.x; idx < GS_SEQS * bw; idx += 256) {
+        const int sq = idx / bw, k = idx % bw;
+        us[idx] = sq < n_here ? u[(long long)(seq0 + sq) * W + blk * bw + k] : 0.0f;
+    }
+    __syncthreads();
+    const int oc = oc0 + lane;
+    float ar[GS_SEQS], ai[GS_SEQS];
+#pragma unroll
+    for (int sq = 0; sq < GS_SEQS; ++sq) ar[sq] = ai[sq] = 0.0f;
+    if (oc < bw) {
+        const int per = (bw + 7) / 8;
+        const int k_end = min(bw, (warp + 1) * per);
+        const float* pr = wr_t + (long long)blk * bw * bw + oc;
+        const float* pi = wi_t + (long long)blk * bw * bw + oc;
+#pragma unroll 4
+        for (int k = warp * per; k < k_end; ++k) {
+            const float r = pr[(long long)k * bw], i = pi[(long long)k * bw];
+#pragma unroll
+            for (int sq = 0; sq < GS_SEQS; ++sq) {
+                const float uv = us[sq * bw + k];
+                ar[sq] = fmaf(uv, r, ar[sq]);
+                ai[sq] = fmaf(uv, i, ai[sq]);
+            }
+        }
+    }
+#pragma unroll
+    for (int sq = 0; sq < GS_SEQS; ++sq) {
+        part[((warp * GS_SEQS + sq) * 2 + 0) * 32 + lane] = ar[sq];
+        part[((warp * GS_SEQS + sq) * 2 + 1) * 32 + lane] = ai[sq];
+    }
+    __syncthreads();
+    // warp w finishes sequence w of the tile
+    const int sq = warp;
+    if (sq >= n_here || oc >= bw) return;
+    float sr = 0.0f, si = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        sr += part[((w * GS_SEQS + sq) * 2 + 0) * 32 + lane];
+        si += part[((w * GS_SEQS + sq) * 2 + 1) * 32 + lane];
+    }
+    const int ch = blk * bw + oc, token = seq0 + sq;
+    const float r = sigmoid_f(sr + br[ch]), gi = sigmoid_f(si + bi[ch]);
+    const float log_a = -c * r * softplus_f(lam[ch]);
+    const float drive = sqrtf(-expm1f(2.0f * log_a)) * gi * us[sq * bw + oc];
+    float* st = state + (long long)slots[token] * state_stride + ch;
+    const float S = fmaf(expf(log_a), *st, drive);
+    *st = S;
+    const float yb = y_bias != nullptr ? y_bias[ch] : 0.0f;
+    out[(long long)token * W + ch] = from_float<T>(S * gelu_tanh_f(y[(long long)token * y_stride + ch] + yb) * out_scale);
+}
+
 }  // namespace mlc
 
 using namespace mlc;
@@ -560,7 +669,10 @@ extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* 
         return 0;
     }
     if ((C + 255) / 256 > 65535) return MLC_ERR_BAD_SIZE;
-    conv_out_kernel<<<dim3((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + 255) / 256), 256, 0, s>>>(a);
+    if (taps <= CONV_MAX_TAPS)
+        conv_out_kernel<<<dim3((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + 255) / 256), 256, 0, s>>>(a);
+    else
+        conv_out_plain_kernel<<<dim3(n_tokens, (C + 255) / 256), 256, 0, s>>>(a);
     MLC_LAUNCH_CHECK();
     if (taps > 1) {
         conv_state_kernel<<<(unsigned)(((long long)n_seqs * C + 255) / 256), 256, 0, s>>>(a);
@@ -646,6 +758,32 @@ extern "C" int mlc_linear_scan(const float* av, const float* drive, const float*
         linear_scan_kernel<float><<<grid, 128, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (float*)out);
     else if (out_dtype == MLC_DTYPE_BF16)
         linear_scan_kernel<bf16><<<grid, 128, 0, s>>>(av, drive, y, y_stride, y_bias, state, state_stride, slots, cu_seqlens, W, out_scale, (bf16*)out);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+// Gates and recurrence for a step in which every sequence brings one token: u float32 [n_seqs][W] (the convolution's
+// output), wr_t / wi_t the gate matrices transposed to [B][in][out]; the state moves one token on.
+extern "C" int mlc_gates_scan_step(const float* u, const float* wr_t, const float* wi_t, const float* br, const float* bi,
+                                   const float* lam, float c, const float* y, long long y_stride, const float* y_bias,
+                                   float* state, long long state_stride, const int* slots, int n_seqs, int W, int B,
+                                   float out_scale, void* out, int out_dtype, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (W <= 0 || B <= 0 || W % B != 0) return MLC_ERR_BAD_SIZE;
+    const int bw = W / B;
+    const size_t smem = (size_t)(GS_SEQS * bw + 8 * GS_SEQS * 2 * 32) * sizeof(float);
+    if (smem > 48 * 1024) return MLC_ERR_UNSUPPORTED;
+    const dim3 grid(B * ((bw + 31) / 32), (n_seqs + GS_SEQS - 1) / GS_SEQS);
+    if (grid.y > 65535) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == MLC_DTYPE_F32)
+        gates_scan_step_kernel<float><<<grid, 256, smem, s>>>(u, wr_t, wi_t, br, bi, lam, c, y, y_stride, y_bias, state, state_stride,
+                                                              slots, n_seqs, W, bw, out_scale, (float*)out);
+    else if (out_dtype == MLC_DTYPE_BF16)
+        gates_scan_step_kernel<bf16><<<grid, 256, smem, s>>>(u, wr_t, wi_t, br, bi, lam, c, y, y_stride, y_bias, state, state_stride,
+                                                             slots, n_seqs, W, bw, out_scale, (bf16*)out);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();

@@ -16,7 +16,7 @@ __all__ = [
     "attention_simt", "silu_mul", "gather_rows", "linear_simt", "argmax", "sample", "uniform_of", "core",
     "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "PinnedCopy", "decode_advance",
     "layernorm", "qk_norm_rope_cache", "softcap", "convert", "causal_conv", "gated_delta_rule", "gated_rmsnorm", "block_gates",
-    "linear_scan",
+    "linear_scan", "gates_scan_step", "gates_scan_step_takes",
 ]
 
 
@@ -98,6 +98,7 @@ def core() -> ctypes.CDLL:
             "mlc_gated_rmsnorm": [P, P, LL, P, F, LL, I, I, P, I, P],
             "mlc_block_gates": [P, P, P, P, P, P, I, I, I, F, P, P, P],
             "mlc_linear_scan": [P, P, P, LL, P, P, LL, P, P, I, I, I, F, P, I, P],
+            "mlc_gates_scan_step": [P, P, P, P, P, P, F, P, LL, P, P, LL, P, I, I, I, F, P, I, P],
             "mlc_qkv_post": [P, P, P, P, P, I, I, I, I, I, P, I, P, P, P, LL, I, I, I, P],
             "mlc_silu_mul": [P, I, I, I, I, P, I, P],
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
@@ -492,6 +493,28 @@ def linear_scan(a: torch.Tensor, drive: torch.Tensor, y: torch.Tensor, y_col: in
                                   step.n_seqs, W, step.max_q_len, float(out_scale), out.data_ptr(), dtype_code(out.dtype),
                                   _stream()),
            "linear recurrence")
+
+
+def gates_scan_step_takes(width: int, blocks: int) -> bool:
+    """Whether the one-token form of gates and recurrence exists for these sizes (its tile of inputs must fit shared memory)."""
+    return (8 * (width // blocks) + 8 * 8 * 2 * 32) * 4 <= 48 * 1024
+
+
+def gates_scan_step(u: torch.Tensor, w_r_t: torch.Tensor, w_i_t: torch.Tensor, b_r: torch.Tensor, b_i: torch.Tensor,
+                    lam: torch.Tensor, c: float, y: torch.Tensor, y_col: int, y_bias: Optional[torch.Tensor],
+                    state: torch.Tensor, step, out_scale: float, out: torch.Tensor) -> None:
+    """`block_gates` and `linear_scan` in one kernel for a step of one token per sequence; the gate matrices come
+    transposed, [B, in, out]."""
+    require_cuda(u, w_r_t, w_i_t, b_r, b_i, lam, y_bias, out)
+    _require_rows(state)
+    n, W = u.shape
+    B = w_r_t.shape[0]
+    assert step.max_q_len == 1 and n == step.n_seqs and out.shape == (n, W) and state.shape[1] == W
+    assert all(t.dtype == torch.float32 for t in (u, w_r_t, w_i_t, b_r, b_i, lam))
+    _check(core().mlc_gates_scan_step(u.data_ptr(), w_r_t.data_ptr(), w_i_t.data_ptr(), b_r.data_ptr(), b_i.data_ptr(),
+                                      lam.data_ptr(), float(c), _columns(y, y_col), y.stride(0), _ptr(y_bias), state.data_ptr(),
+                                      state.stride(0), step.slots.data_ptr(), n, W, B, float(out_scale), out.data_ptr(),
+                                      dtype_code(out.dtype), _stream()), "recurrence gates and step")
 
 
 class PinnedCopy:

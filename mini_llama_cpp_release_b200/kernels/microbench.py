@@ -186,6 +186,86 @@ def bench_norm(args) -> None:
            T * K * (8 + 4 * S + 2), 0.0)
 
 
+def _step(lens, device=DEV):
+    """A step's description for sequences of `lens` new tokens in slots 0, 1, ... (what the recurrent kernels read of it)."""
+    from ..engine.step_info import StepInfo
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    return StepInfo(n_tokens=cu[-1], n_seqs=len(lens), max_q_len=max(lens), max_kv_len=0, tokens=i32([0] * cu[-1]),
+                    positions=i32([p for n in lens for p in range(n)]), tok_seq=i32([b for b, n in enumerate(lens) for _ in range(n)]),
+                    cu_seqlens=i32(cu), start_pos=i32([0] * len(lens)), slots=i32(list(range(len(lens)))), want_rows=i32([]),
+                    page_tables=[])
+
+
+def bench_recurrent(args) -> None:
+    """The kernels of the mixers with state, and the norms around them, at `--seqs` sequences of `--tokens / --seqs` new
+    tokens each: layernorm (of a branch, with the 16-bit copy), conv (C = --k channels, --taps), delta (--heads, --kv-heads,
+    --head-dim for keys and values), gates and scan (W = --k channels, --blocks), qknorm (per-head norm, rotation, cache write)."""
+    T, B = args.tokens, args.seqs
+    lens = [T // B] * B
+    T = sum(lens)
+    step = _step(lens)
+    name = args.kernel
+    if name == "layernorm":
+        d = args.k
+        x, y, g = torch.randn(T, d, device=DEV), torch.randn(T, d, device=DEV), torch.ones(d, device=DEV)
+        out = torch.empty(T, d, dtype=torch.bfloat16, device=DEV)
+        report(f"layernorm of a branch T={T} d={d}", lambda i: kernels.layernorm(x, y, g, 1e-6, out, of_branch=True), args,
+               T * d * (4 + 4 + 4 + 2), 0.0)
+    elif name == "conv":
+        C, taps = args.k, args.taps
+        x, w = torch.randn(T, C + 64, device=DEV), torch.randn(C, taps, device=DEV)
+        state, out = torch.zeros(B, (taps - 1) * C, device=DEV), torch.empty(T, C, device=DEV)
+        report(f"causal conv T={T} C={C} taps={taps}", lambda i: kernels.causal_conv(x, 0, w, None, True, state, step, out), args,
+               T * C * 8, 2.0 * T * C * taps)
+    elif name == "delta":
+        H, G, dim = args.heads, args.kv_heads, args.head_dim
+        qkv = torch.randn(T, 2 * G * dim + H * dim, device=DEV)
+        gates = torch.randn(T, 2 * H, device=DEV)
+        A_log, dt = torch.zeros(H, device=DEV) - 3.0, torch.zeros(H, device=DEV)
+        state, out = torch.zeros(B, H * dim * dim, device=DEV), torch.empty(T, H * dim, device=DEV)
+        report(f"gated delta rule T={T} seqs={B} H={H} G={G} dim={dim}",
+               lambda i: kernels.gated_delta_rule(qkv, 0, G * dim, 2 * G * dim, gates, 0, H, A_log, dt, state, step, H, G, dim, dim, out),
+               args, T * (2 * G * dim + 2 * H * dim) * 4 + 2 * B * H * dim * dim * 4, 8.0 * T * H * dim * dim)
+    elif name in ("gates", "scan"):
+        W, nb = args.k, args.blocks
+        u = torch.randn(T, W, device=DEV)
+        wr, wi = torch.randn(nb, W // nb, W // nb, device=DEV) * 0.1, torch.randn(nb, W // nb, W // nb, device=DEV) * 0.1
+        br, bi, lam = torch.zeros(W, device=DEV), torch.zeros(W, device=DEV), torch.zeros(W, device=DEV) - 3.0
+        a, drive = torch.empty(T, W, device=DEV), torch.empty(T, W, device=DEV)
+        kernels.block_gates(u, wr, wi, br, bi, lam, 8.0, a, drive)
+        if name == "gates":
+            report(f"recurrence gates T={T} W={W} blocks={nb}", lambda i: kernels.block_gates(u, wr, wi, br, bi, lam, 8.0, a, drive),
+                   args, T * W * 12 + 2 * W * (W // nb) * 4, 4.0 * T * W * (W // nb))
+        else:
+            y, state = torch.randn(T, W, device=DEV), torch.zeros(B, W, device=DEV)
+            out = torch.empty(T, W, dtype=torch.bfloat16, device=DEV)
+            report(f"linear recurrence T={T} seqs={B} W={W}", lambda i: kernels.linear_scan(a, drive, y, 0, None, state, step, 1.0, out),
+                   args, T * W * 14, 0.0)
+    else:
+        H, KV, hd = args.heads, args.kv_heads, args.head_dim
+        proj = torch.randn(T, (H + 2 * KV) * hd, device=DEV)
+        gain = torch.ones(hd, device=DEV)
+        pages = (max(lens) + 63) // 64
+        pool_k = torch.empty(1, B * pages, KV, 64, hd, dtype=torch.bfloat16, device=DEV)
+        pool_v = torch.empty_like(pool_k)
+        table = torch.arange(B * pages, dtype=torch.int32, device=DEV).view(B, pages)
+        kv = bindings.KVView(pool_k, pool_v, 0, table, 64, KV, hd)
+        rope = kernels.rope_table(torch.rand(hd // 4, device=DEV), max(lens))
+        q = torch.empty(T, H * hd, dtype=torch.bfloat16, device=DEV)
+        nbytes = T * (H + 2 * KV) * hd * 6
+        if name == "qknorm":
+            report(f"q/k norm, rotation, cache write T={T} H={H} KV={KV} hd={hd}",
+                   lambda i: kernels.qk_norm_rope_cache(proj, 0, H * hd, (H + KV) * hd, gain, gain, 1e-6, step.positions, step.tok_seq,
+                                                        rope, hd // 2, H, KV, hd, hd, 1.0, q, kv), args, nbytes, 0.0)
+        else:
+            full = kernels.rope_table(torch.rand(hd // 2, device=DEV), max(lens))
+            report(f"q/k/v bias, rotation, cache write T={T} H={H} KV={KV} hd={hd}",
+                   lambda i: kernels.qkv_post(proj, None, step.positions, step.tok_seq, full, H, KV, hd, q, kv), args, nbytes, 0.0)
+
+
 def bench_attention(args) -> None:
     B, L, H, KV, hd, C = args.seqs, args.context, args.heads, args.kv_heads, args.head_dim, args.copies
     q_len = args.q_len
@@ -276,7 +356,9 @@ def decode_phases(args, fn, blocks: int, n_splits: int) -> None:
 
 def parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "norm", "attention"])
+    ap.add_argument("kernel", choices=["gemm", "norm", "attention", "layernorm", "conv", "delta", "gates", "scan", "qknorm", "qkvpost"])
+    ap.add_argument("--taps", type=int, default=4)
+    ap.add_argument("--blocks", type=int, default=12)
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--rows", type=int, default=9728)
     ap.add_argument("--k", type=int, default=896)
@@ -312,8 +394,10 @@ def main(argv=None) -> int:
         bench_gemm(args)
     elif args.kernel == "norm":
         bench_norm(args)
-    else:
+    elif args.kernel == "attention":
         bench_attention(args)
+    else:
+        bench_recurrent(args)
     return 0
 
 

@@ -158,6 +158,9 @@ class GatedLinearRecurrence(Part):
         self.y_bias, self.x_bias = _f32(get(t["y_bias"])), _f32(get(t["x_bias"]))
         self.conv_w, self.conv_bias = _f32(get(t["conv"])), _f32(get(t["conv_bias"]))
         self.w_r, self.w_i = _f32(get(t["r"])), _f32(get(t["i"]))
+        # for steps of one token per sequence: [block][in][out], so that neighbouring outputs lie side by side
+        self.w_r_t, self.w_i_t = self.w_r.transpose(1, 2).contiguous(), self.w_i.transpose(1, 2).contiguous()
+        self.one_token_form = kernels.gates_scan_step_takes(self.W, self.B)
         self.b_r, self.b_i = _f32(get(t["r_bias"])).view(-1), _f32(get(t["i_bias"])).view(-1)
         self.lam = _f32(get(t["lam"]))
         self.o = Linear(get(t["o"]), runtime)
@@ -180,9 +183,13 @@ class GatedLinearRecurrence(Part):
         S, conv_state = memory.state[:, :W], memory.state[:, W:]
         u = rt.empty(n, W, dtype=torch.float32)
         kernels.causal_conv(proj, col + W, self.conv_w, self.conv_bias, False, conv_state, step, u, in_bias=self.x_bias)
+        act = rt.empty(n, W)
+        if step.max_q_len == 1 and n == step.n_seqs and self.one_token_form:
+            kernels.gates_scan_step(u, self.w_r_t, self.w_i_t, self.b_r, self.b_i, self.lam, self.DECAY_CONSTANT, proj, col,
+                                    self.y_bias, S, step, self.out_scale, act)
+            return act
         a, drive = rt.empty(n, W, dtype=torch.float32), rt.empty(n, W, dtype=torch.float32)
         kernels.block_gates(u, self.w_r, self.w_i, self.b_r, self.b_i, self.lam, self.DECAY_CONSTANT, a, drive)
-        act = rt.empty(n, W)
         kernels.linear_scan(a, drive, proj, col, self.y_bias, S, step, self.out_scale, act)
         return act
 

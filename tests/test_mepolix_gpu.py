@@ -256,7 +256,7 @@ def step_of(lens, slots, device="cuda"):
                     slots=i32(slots), want_rows=i32([]), page_tables=[])
 
 
-@pytest.mark.parametrize("taps, silu", [(4, True), (2, False), (1, True), (7, False)])
+@pytest.mark.parametrize("taps, silu", [(4, True), (2, False), (1, True), (7, False), (11, True)])
 def test_causal_convolution_carries_its_last_inputs(taps, silu):
     g = torch.Generator().manual_seed(taps)
     C, pad = 37, 5                                       # channels are a column range of wider rows
@@ -373,3 +373,28 @@ def test_layer_norm_of_the_stream_and_of_a_branch(d):
     kernels.layernorm(xs, y.cuda()[0].contiguous(), w.cuda(), 1e-5, out, of_branch=False)
     assert torch.allclose(xs.cpu(), x + y[0], atol=1e-6)
     assert torch.allclose(out.cpu().double(), pm.layer_norm((x + y[0]).double(), w.double(), 1e-5), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("W, B, n_seqs", [(96, 3, 1), (64, 1, 11), (40, 5, 8), (200, 2, 9)])
+def test_one_token_form_of_gates_and_recurrence(W, B, n_seqs):
+    g = torch.Generator().manual_seed(W + n_seqs)
+    bw = W // B
+    u = torch.randn(n_seqs, W, generator=g)
+    wr, wi = torch.randn(B, bw, bw, generator=g) * 0.3, torch.randn(B, bw, bw, generator=g) * 0.3
+    br, bi, lam = torch.randn(W, generator=g), torch.randn(W, generator=g), torch.randn(W, generator=g) - 3.0
+    y, yb = torch.randn(n_seqs, W + 4, generator=g), torch.randn(W, generator=g)
+    slots = list(range(n_seqs + 2))[::-1][:n_seqs]
+    state = torch.randn(n_seqs + 2, W, generator=g)
+    dev_state = state.cuda()
+    out = torch.empty(n_seqs, W, device="cuda")
+    kernels.gates_scan_step(u.cuda(), wr.transpose(1, 2).contiguous().cuda(), wi.transpose(1, 2).contiguous().cuda(), br.cuda(),
+                            bi.cuda(), lam.cuda(), 8.0, y.cuda(), 2, yb.cuda(), dev_state, step_of([1] * n_seqs, slots), 1.25, out)
+    ud = u.double().view(n_seqs, B, bw)
+    r = torch.sigmoid(torch.einsum("tbi,boi->tbo", ud, wr.double()).reshape(n_seqs, W) + br.double())
+    i = torch.sigmoid(torch.einsum("tbi,boi->tbo", ud, wi.double()).reshape(n_seqs, W) + bi.double())
+    a = torch.exp(-8.0 * r * torch.nn.functional.softplus(lam.double()))
+    S = a * state[slots].double() + torch.sqrt(1.0 - a * a) * i * u.double()
+    assert torch.allclose(dev_state[slots].cpu().double(), S, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(out.cpu().double(), S * pm.gelu_tanh(y[:, 2:2 + W].double() + yb.double()) * 1.25, atol=1e-5, rtol=1e-4)
+    untouched = [s for s in range(n_seqs + 2) if s not in slots]
+    assert torch.equal(dev_state[untouched].cpu(), state[untouched])
