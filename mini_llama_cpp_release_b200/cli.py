@@ -269,6 +269,12 @@ def cmd_inspect(argv: Sequence[str]) -> int:
     needs = [m.cache_need() if hasattr(m, "cache_need") else None for m in mixers]
     kv = cache_bytes_per_token(needs, [e.reads_cache_of for e in spec.schedule], 1)
     print(f"cache per token per sequence: {kv * 2} B in bfloat16, {kv * 4} B in float32")
+    # fixed-size state of the mixers that keep one (recurrences, convolutions), whatever the sequence's length
+    import math
+    import torch
+    states = [m.state_spec() if hasattr(m, "state_spec") else None for m in mixers]
+    state_bytes = sum(math.prod(st.shape) * torch.empty((), dtype=st.dtype).element_size() for st in states if st is not None)
+    print(f"state per sequence: {state_bytes} B in {sum(st is not None for st in states)} of {len(mixers)} runs")
     for line in problems:
         print("PROBLEM:", line)
     return 1 if problems else 0

@@ -92,3 +92,23 @@ def test_plain_pieces_against_textbook_forms():
     assert torch.allclose(r[..., 4:], torch.ones(4, 1, 4, dtype=torch.float64))
     assert torch.allclose(r[..., 0] ** 2 + r[..., 2] ** 2, torch.full((4, 1), 2.0, dtype=torch.float64))
     assert math.isclose(float(r[1, 0, 0]), math.cos(1.0) - math.sin(1.0), rel_tol=1e-6)
+
+
+def test_inspect_and_random_weights_on_the_command_line(tmp_path):
+    """Random weights of the design are written without a GPU, and `inspect` reads them back: the schedule with its
+    second run, the cache of the attention runs and the state of every run."""
+    import subprocess
+    import sys
+    import os
+    import mini_llama_cpp_release_b200 as ml
+    folder = ml.write_random_model(ModelConfig.from_dict(mh.MIXED), str(tmp_path / "m"), seed=3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "mini_llama_cpp_release_b200", "inspect", folder], capture_output=True, text=True, cwd=root)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert "architecture: Mepolix -> 3 layers, 4 runs per step" in p.stdout
+    assert "l0.mix.left.sink" in p.stdout and "PROBLEM" not in p.stdout
+    # two attention runs of 2 kv heads x 32 entries (keys and values), in bfloat16
+    assert f"cache per token per sequence: {2 * 2 * 2 * 32 * 2} B in bfloat16" in p.stdout
+    # parallel: 96 channels x 4 taps; delta: 4 x 16 x 24 + 1 x (32 + 32 + 96); delta: 3 x 40 x 20 + 2 x (120 + 120 + 60)
+    want = 4 * (2 * 96 * 4 + (4 * 16 * 24 + 160) + (3 * 40 * 20 + 2 * 300))
+    assert f"state per sequence: {want} B in 4 of 4 runs" in p.stdout
