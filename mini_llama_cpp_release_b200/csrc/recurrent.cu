@@ -14,8 +14,11 @@ namespace mlc {
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+// gelu_tanh(z) = 0.5 z (1 + tanh(w)), w = sqrt(2/pi) (z + 0.044715 z³).  Since 1 + tanh(w) = 2 / (1 + exp(-2w)), it is
+// formed as z / (1 + exp(-2w)): the sum 1 + tanh(w) would lose its digits where tanh(w) is close to -1.
 __device__ __forceinline__ float gelu_tanh_f(float z) {
-    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float w = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return z / (1.0f + expf(-2.0f * w));
 }
 
 // ------------------------------------------------------------------ causal convolution
