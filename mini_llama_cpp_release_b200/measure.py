@@ -32,7 +32,7 @@ def _mepolix(width: int, ff: int, heads: int, kv_heads: int, head: int, n_layers
              "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": head, "vdim": head, "conv": 4}}
     par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
-                              "rot": {"dims": head // 2, "base": 500000.0,
+                              "rot": {"dims": head // 2, "base": 1000000.0,
                                       "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
                      "right": {"width": width, "blocks": max(1, width // 128), "conv": 4},
                      "left_scale": 1.0, "right_scale": 1.0}}
