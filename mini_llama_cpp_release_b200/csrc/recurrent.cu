@@ -185,6 +185,7 @@ struct DeltaArgs {
     float* out;                 // [n_tokens][H * vdim]
     int H, G, dim, vdim, n_tokens;
     float q_scale;              // dim^-1/2
+    int vec4;                   // rows, columns and sizes allow 16-byte copies of q, k and v
 };
 
 __global__ void delta_prepare_kernel(DeltaArgs a) {
@@ -214,6 +215,11 @@ __global__ void delta_prepare_kernel(DeltaArgs a) {
         c[3] = fq;
         c[4] = skq * fk * fq;
     }
+}
+
+__device__ __forceinline__ void cp_async_f32x4(float* smem, const float* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
 }
 
 __device__ __forceinline__ void cp_async_f32(float* smem, const float* gmem) {
@@ -361,6 +367,330 @@ static cudaError_t launch_delta_rule(const DeltaArgs& a, dim3 grid, cudaStream_t
         raised = true;
     }
     delta_rule_kernel<NI><<<grid, 128, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
+
+// ------------------------------------------------------------------ gated delta rule, four tokens a round
+// The walk above pays the latency of one round (shared-memory reads, products, shuffles, update) per token.  Four
+// tokens can share a round: with S the state before the group, G_t the product of the group's decays up to token t,
+// P_ts the product of the decays after s up to t, and k̂, q̂ the unit vectors,
+//     u_t = beta_t (v_t − G_t Sᵀk̂_t − sum_{s<t} P_ts (k̂_s·k̂_t) u_s)
+//     o_t = G_t Sᵀq̂_t + sum_{s<=t} P_ts (k̂_s·q̂_t) u_s
+//     S  <- G_3 S + sum_t P_3t k̂_t u_tᵀ
+// (the state after token t is G_t S + sum_{s<=t} P_ts k̂_s u_sᵀ, which put into the rule for token t+1 gives these).
+// All eight products of a round with S (four with k, four with q) are independent, their shuffles overlap, and the u_t
+// follow from each other by a few scalar operations.  The first kernel leaves, per (token, head), the sixteen numbers
+// of a token's place in its group; a group's missing tokens at a sequence's end count as tokens that change nothing
+// (beta = 0, decay 1).  Groups are counted from the sequence's first token of the step.
+constexpr int DG = 4;            // tokens per round
+constexpr int DG_COEF = 16;      // [0] G_t fk_t, [1] G_t fq_t, [2] beta_t, [3] P_3t fk_t, [4..6] P_ts k̂_s·k̂_t (s < t), [7] G_3, [8..11] P_ts k̂_s·q̂_t (s <= t)
+
+// Records are kept per sequence with room for a last group's missing tokens: sequence b's token t is record
+// cu_seqlens[b] + 3 b + t.
+__global__ void __launch_bounds__(128)
+delta_prepare_group_kernel(DeltaArgs a) {
+    const int seq = blockIdx.z, group = blockIdx.x;
+    const int head = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int first = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - first;
+    if (group * DG >= q_len || head >= a.H) return;
+    const int kv_head = head / (a.H / a.G);
+    const int n_t = min(DG, q_len - group * DG);
+    float nk[DG], nq[DG], kk[DG][DG], kq[DG][DG];
+#pragma unroll
+    for (int t = 0; t < DG; ++t) {
+        nk[t] = nq[t] = 0.0f;
+#pragma unroll
+        for (int u = 0; u < DG; ++u) kk[t][u] = kq[t][u] = 0.0f;
+    }
+    for (int i = lane; i < a.dim; i += 32) {
+        float kv[DG], qv[DG];
+#pragma unroll
+        for (int t = 0; t < DG; ++t) {
+            const float* row = a.qkv + (long long)(first + group * DG + t) * a.qkv_stride + kv_head * a.dim + i;
+            kv[t] = t < n_t ? row[a.k_col] : 0.0f;
+            qv[t] = t < n_t ? row[a.q_col] : 0.0f;
+        }
+#pragma unroll
+        for (int t = 0; t < DG; ++t) {
+            nk[t] = fmaf(kv[t], kv[t], nk[t]);
+            nq[t] = fmaf(qv[t], qv[t], nq[t]);
+#pragma unroll
+            for (int u = 0; u < DG; ++u) {
+                if (u < t) kk[u][t] = fmaf(kv[u], kv[t], kk[u][t]);
+                if (u <= t) kq[u][t] = fmaf(kv[u], qv[t], kq[u][t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < DG; ++t) {
+        nk[t] = warp_sum(nk[t]);
+        nq[t] = warp_sum(nq[t]);
+#pragma unroll
+        for (int u = 0; u < DG; ++u) {
+            if (u < t) kk[u][t] = warp_sum(kk[u][t]);
+            if (u <= t) kq[u][t] = warp_sum(kq[u][t]);
+        }
+    }
+    float g[DG], beta[DG], fk[DG], fq[DG];
+    const float neg_rate = -expf(a.A_log[head]), dt_bias = a.dt_bias[head];
+#pragma unroll
+    for (int t = 0; t < DG; ++t) {
+        if (t < n_t) {
+            const float* gr = a.gates + (long long)(first + group * DG + t) * a.gates_stride;
+            g[t] = expf(neg_rate * softplus_f(gr[a.a_col + head] + dt_bias));
+            beta[t] = sigmoid_f(gr[a.b_col + head]);
+            fk[t] = 1.0f / sqrtf(nk[t] + 1e-6f);
+            fq[t] = a.q_scale / sqrtf(nq[t] + 1e-6f);
+        } else {
+            g[t] = 1.0f;
+            beta[t] = fk[t] = fq[t] = 0.0f;
+        }
+    }
+    if (lane < DG) {
+        const int t = lane;
+        float P[DG];                                  // P[s] = product of g over s+1 .. t (1 for s = t)
+        float run = 1.0f;
+#pragma unroll
+        for (int s = DG - 1; s >= 0; --s) {
+            if (s <= t) {
+                P[s] = run;
+                run *= g[s];
+            } else {
+                P[s] = 0.0f;
+            }
+        }
+        const float G_t = run;                       // g_0 .. g_t
+        float after = 1.0f;                           // product of g over t+1 .. 3
+        float G3 = 1.0f;
+#pragma unroll
+        for (int s = 0; s < DG; ++s) {
+            G3 *= g[s];
+            if (s > t) after *= g[s];
+        }
+        // select this lane's token's numbers without indexing registers by a variable
+        float fk_t = 0.0f, fq_t = 0.0f, beta_t = 0.0f, A[DG], B[DG];
+#pragma unroll
+        for (int u = 0; u < DG; ++u) A[u] = B[u] = 0.0f;
+#pragma unroll
+        for (int tt = 0; tt < DG; ++tt) {
+            if (tt == t) {
+                fk_t = fk[tt];
+                fq_t = fq[tt];
+                beta_t = beta[tt];
+#pragma unroll
+                for (int u = 0; u < DG; ++u) {
+                    if (u < tt) A[u] = P[u] * fk[u] * fk[tt] * kk[u][tt];
+                    if (u <= tt) B[u] = P[u] * fk[u] * fq[tt] * kq[u][tt];
+                }
+            }
+        }
+        float* c = a.coef + ((long long)(first + 3 * seq + group * DG + t) * a.H + head) * DG_COEF;
+        c[0] = G_t * fk_t;
+        c[1] = G_t * fq_t;
+        c[2] = beta_t;
+        c[3] = after * fk_t;
+        c[4] = A[0]; c[5] = A[1]; c[6] = A[2];
+        c[7] = G3;
+        c[8] = B[0]; c[9] = B[1]; c[10] = B[2]; c[11] = B[3];
+    }
+}
+
+template <int NI>
+struct DeltaGroupSmem {
+    static constexpr int ROW = 8 * (NI + 4);
+    float k[DR_CHUNK][ROW];
+    float q[DR_CHUNK][ROW];
+    float v[DR_CHUNK][DR_COLS];
+    float coef[DR_CHUNK][DG_COEF];
+};
+
+template <int NI>
+__global__ void __launch_bounds__(128)
+delta_rule_group_kernel(DeltaArgs a) {
+    static_assert(NI % 4 == 0 && DR_CHUNK % DG == 0, "rows per lane come in fours, groups do not straddle chunks");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    DeltaGroupSmem<NI>* bufs = reinterpret_cast<DeltaGroupSmem<NI>*>(smem_raw);
+
+    const int seq = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * DR_COLS;
+    const int kv_head = head / (a.H / a.G);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int part = lane >> 2;
+    const int col_in_block = warp * 8 + (lane & 3) * 2;
+    const int col = col0 + col_in_block;
+    const bool ok0 = col < a.vdim, ok1 = col + 1 < a.vdim;
+    const int first = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - first;
+    float* S_glob = a.state + (long long)a.slots[seq] * a.state_stride + (long long)head * a.dim * a.vdim;
+
+    float S0[NI], S1[NI];
+#pragma unroll
+    for (int ii = 0; ii < NI; ++ii) {
+        const int i = part * NI + ii;
+        S0[ii] = (ok0 && i < a.dim) ? S_glob[(long long)i * a.vdim + col] : 0.0f;
+        S1[ii] = (ok1 && i < a.dim) ? S_glob[(long long)i * a.vdim + col + 1] : 0.0f;
+    }
+
+    auto fetch = [&](int t0, DeltaGroupSmem<NI>& b) {
+        const int n_t = min(DR_CHUNK, q_len - t0);
+        const int n_rec = min(DR_CHUNK, (n_t + DG - 1) / DG * DG);       // a last group's missing tokens have records too
+        if (a.vec4) {                                                      // 16 bytes a copy: a quarter of the copies
+            for (int idx = tid; idx < DR_CHUNK * 2 * NI; idx += 128) {
+                const int t = idx / (2 * NI), i = (idx % (2 * NI)) * 4;
+                const int at = i + 4 * (i / NI);
+                if (t < n_t && i < a.dim) {
+                    const float* row = a.qkv + (long long)(first + t0 + t) * a.qkv_stride + kv_head * a.dim + i;
+                    cp_async_f32x4(&b.k[t][at], row + a.k_col);
+                    cp_async_f32x4(&b.q[t][at], row + a.q_col);
+                } else {
+                    *reinterpret_cast<float4*>(&b.k[t][at]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    *reinterpret_cast<float4*>(&b.q[t][at]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
+            for (int idx = tid; idx < DR_CHUNK * DR_COLS / 4; idx += 128) {
+                const int t = idx / (DR_COLS / 4), j = (idx % (DR_COLS / 4)) * 4;
+                if (t < n_t && col0 + j < a.vdim)
+                    cp_async_f32x4(&b.v[t][j], a.qkv + (long long)(first + t0 + t) * a.qkv_stride + a.v_col + head * a.vdim + col0 + j);
+                else
+                    *reinterpret_cast<float4*>(&b.v[t][j]) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        } else {
+            for (int idx = tid; idx < DR_CHUNK * 8 * NI; idx += 128) {
+                const int t = idx / (8 * NI), i = idx % (8 * NI);
+                const int at = i + 4 * (i / NI);
+                if (t < n_t && i < a.dim) {
+                    const float* row = a.qkv + (long long)(first + t0 + t) * a.qkv_stride + kv_head * a.dim + i;
+                    cp_async_f32(&b.k[t][at], row + a.k_col);
+                    cp_async_f32(&b.q[t][at], row + a.q_col);
+                } else {
+                    b.k[t][at] = 0.0f;
+                    b.q[t][at] = 0.0f;
+                }
+            }
+            for (int idx = tid; idx < DR_CHUNK * DR_COLS; idx += 128) {
+                const int t = idx / DR_COLS, j = idx % DR_COLS;
+                if (t < n_t && col0 + j < a.vdim)
+                    cp_async_f32(&b.v[t][j], a.qkv + (long long)(first + t0 + t) * a.qkv_stride + a.v_col + head * a.vdim + col0 + j);
+                else
+                    b.v[t][j] = 0.0f;
+            }
+        }
+        for (int idx = tid; idx < DR_CHUNK * 3; idx += 128) {             // records are 64 bytes apart: always aligned
+            const int t = idx / 3, e = (idx % 3) * 4;
+            if (t < n_rec) cp_async_f32x4(&b.coef[t][e], a.coef + ((long long)(first + 3 * seq + t0 + t) * a.H + head) * DG_COEF + e);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    fetch(0, bufs[0]);
+    int cur = 0;
+    for (int t0 = 0; t0 < q_len; t0 += DR_CHUNK, cur ^= 1) {
+        const int n_t = min(DR_CHUNK, q_len - t0);
+        DeltaGroupSmem<NI>& b = bufs[cur];
+        if (t0 + DR_CHUNK < q_len) {
+            fetch(t0 + DR_CHUNK, bufs[cur ^ 1]);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();
+        for (int g0 = 0; g0 < n_t; g0 += DG) {
+            float kr[DG][NI];
+            float dk0[DG], dk1[DG], dq0[DG], dq1[DG];
+#pragma unroll
+            for (int j = 0; j < DG; ++j) {
+                const float4* k4 = reinterpret_cast<const float4*>(&b.k[g0 + j][part * (NI + 4)]);
+                const float4* q4 = reinterpret_cast<const float4*>(&b.q[g0 + j][part * (NI + 4)]);
+                dk0[j] = dk1[j] = dq0[j] = dq1[j] = 0.0f;
+#pragma unroll
+                for (int v = 0; v < NI / 4; ++v) {
+                    const float4 kk = k4[v], qq = q4[v];
+                    kr[j][4 * v] = kk.x; kr[j][4 * v + 1] = kk.y; kr[j][4 * v + 2] = kk.z; kr[j][4 * v + 3] = kk.w;
+                    dk0[j] = fmaf(S0[4 * v], kk.x, dk0[j]);     dk1[j] = fmaf(S1[4 * v], kk.x, dk1[j]);
+                    dq0[j] = fmaf(S0[4 * v], qq.x, dq0[j]);     dq1[j] = fmaf(S1[4 * v], qq.x, dq1[j]);
+                    dk0[j] = fmaf(S0[4 * v + 1], kk.y, dk0[j]); dk1[j] = fmaf(S1[4 * v + 1], kk.y, dk1[j]);
+                    dq0[j] = fmaf(S0[4 * v + 1], qq.y, dq0[j]); dq1[j] = fmaf(S1[4 * v + 1], qq.y, dq1[j]);
+                    dk0[j] = fmaf(S0[4 * v + 2], kk.z, dk0[j]); dk1[j] = fmaf(S1[4 * v + 2], kk.z, dk1[j]);
+                    dq0[j] = fmaf(S0[4 * v + 2], qq.z, dq0[j]); dq1[j] = fmaf(S1[4 * v + 2], qq.z, dq1[j]);
+                    dk0[j] = fmaf(S0[4 * v + 3], kk.w, dk0[j]); dk1[j] = fmaf(S1[4 * v + 3], kk.w, dk1[j]);
+                    dq0[j] = fmaf(S0[4 * v + 3], qq.w, dq0[j]); dq1[j] = fmaf(S1[4 * v + 3], qq.w, dq1[j]);
+                }
+            }
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) {
+#pragma unroll
+                for (int j = 0; j < DG; ++j) {
+                    dk0[j] += __shfl_xor_sync(0xffffffffu, dk0[j], o);
+                    dk1[j] += __shfl_xor_sync(0xffffffffu, dk1[j], o);
+                    dq0[j] += __shfl_xor_sync(0xffffffffu, dq0[j], o);
+                    dq1[j] += __shfl_xor_sync(0xffffffffu, dq1[j], o);
+                }
+            }
+            float u0[DG], u1[DG], w0[DG], w1[DG];
+            float G3 = 1.0f;
+#pragma unroll
+            for (int t = 0; t < DG; ++t) {
+                const float4 c0 = *reinterpret_cast<const float4*>(&b.coef[g0 + t][0]);     // G fk, G fq, beta, P_3t fk
+                const float4 c1 = *reinterpret_cast<const float4*>(&b.coef[g0 + t][4]);     // A[0..2], G_3
+                const float4 c2 = *reinterpret_cast<const float4*>(&b.coef[g0 + t][8]);     // B[0..3]
+                const float2 vv = *reinterpret_cast<const float2*>(&b.v[g0 + t][col_in_block]);
+                const float A[3] = {c1.x, c1.y, c1.z};
+                const float B[4] = {c2.x, c2.y, c2.z, c2.w};
+                float r0 = vv.x - c0.x * dk0[t], r1 = vv.y - c0.x * dk1[t];
+                float o0 = c0.y * dq0[t], o1 = c0.y * dq1[t];
+#pragma unroll
+                for (int sidx = 0; sidx < DG; ++sidx) {
+                    if (sidx < t) {
+                        r0 = fmaf(-A[sidx], u0[sidx], r0);
+                        r1 = fmaf(-A[sidx], u1[sidx], r1);
+                        o0 = fmaf(B[sidx], u0[sidx], o0);
+                        o1 = fmaf(B[sidx], u1[sidx], o1);
+                    }
+                }
+                u0[t] = c0.z * r0;
+                u1[t] = c0.z * r1;
+                o0 = fmaf(B[t], u0[t], o0);
+                o1 = fmaf(B[t], u1[t], o1);
+                w0[t] = c0.w * u0[t];
+                w1[t] = c0.w * u1[t];
+                G3 = c1.w;
+                if (part == 0 && g0 + t < n_t) {
+                    float* o = a.out + (long long)(first + t0 + g0 + t) * a.H * a.vdim + (long long)head * a.vdim + col;
+                    if (ok0) o[0] = o0;
+                    if (ok1) o[1] = o1;
+                }
+            }
+#pragma unroll
+            for (int ii = 0; ii < NI; ++ii) {
+                float s0 = G3 * S0[ii], s1 = G3 * S1[ii];
+#pragma unroll
+                for (int t = 0; t < DG; ++t) {
+                    s0 = fmaf(kr[t][ii], w0[t], s0);
+                    s1 = fmaf(kr[t][ii], w1[t], s1);
+                }
+                S0[ii] = s0;
+                S1[ii] = s1;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int ii = 0; ii < NI; ++ii) {
+        const int i = part * NI + ii;
+        if (ok0 && i < a.dim) S_glob[(long long)i * a.vdim + col] = S0[ii];
+        if (ok1 && i < a.dim) S_glob[(long long)i * a.vdim + col + 1] = S1[ii];
+    }
+}
+
+template <int NI>
+static cudaError_t launch_delta_rule_group(const DeltaArgs& a, dim3 grid, cudaStream_t s) {
+    const size_t smem = 2 * sizeof(DeltaGroupSmem<NI>);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e = cudaFuncSetAttribute(delta_rule_group_kernel<NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        raised = true;
+    }
+    delta_rule_group_kernel<NI><<<grid, 128, smem, s>>>(a);
     return cudaGetLastError();
 }
 
@@ -684,21 +1014,34 @@ extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* 
     return 0;
 }
 
-// coef: scratch of n_tokens * H * 5 floats.
+// coef: scratch of (n_tokens + 3 * n_seqs) * H * 16 floats.  max_q_len: the longest run of new tokens of any sequence.
 extern "C" int mlc_gated_delta_rule(const float* qkv, long long qkv_stride, int q_col, int k_col, int v_col, const float* gates,
                                     long long gates_stride, int b_col, int a_col, const float* A_log, const float* dt_bias,
                                     float* coef, float* state, long long state_stride, const int* slots, const int* cu_seqlens,
-                                    int n_seqs, int n_tokens, int H, int G, int dim, int vdim, float* out, void* stream) {
+                                    int n_seqs, int n_tokens, int max_q_len, int H, int G, int dim, int vdim, float* out,
+                                    void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || dim <= 0 || dim > 256 || vdim <= 0 || n_seqs > 65535 || H > 65535) return MLC_ERR_BAD_SIZE;
     DeltaArgs a{qkv, qkv_stride, q_col, k_col, v_col, gates, gates_stride, b_col, a_col, A_log, dt_bias, coef, state, state_stride,
-                slots, cu_seqlens, out, H, G, dim, vdim, n_tokens, 1.0f / sqrtf((float)dim)};
+                slots, cu_seqlens, out, H, G, dim, vdim, n_tokens, 1.0f / sqrtf((float)dim), 0};
+    a.vec4 = ((dim | vdim | q_col | k_col | v_col) % 4 == 0 && qkv_stride % 4 == 0 && ((uintptr_t)qkv | (uintptr_t)coef) % 16 == 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    delta_prepare_kernel<<<(unsigned)(((long long)n_tokens * H + 7) / 8), 256, 0, s>>>(a);
-    MLC_LAUNCH_CHECK();
     const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, n_seqs);
     const int ni = (dim + 7) / 8;
     cudaError_t e;
+    if (max_q_len >= DG && ni <= 16) {                    // runs of tokens: four a round (key sizes up to 128)
+        const dim3 pgrid((max_q_len + DG - 1) / DG, (H + 3) / 4, n_seqs);
+        if (pgrid.y > 65535) return MLC_ERR_BAD_SIZE;
+        delta_prepare_group_kernel<<<pgrid, 128, 0, s>>>(a);
+        MLC_LAUNCH_CHECK();
+        if (ni <= 4) e = launch_delta_rule_group<4>(a, grid, s);
+        else if (ni <= 8) e = launch_delta_rule_group<8>(a, grid, s);
+        else if (ni <= 12) e = launch_delta_rule_group<12>(a, grid, s);
+        else e = launch_delta_rule_group<16>(a, grid, s);
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    delta_prepare_kernel<<<(unsigned)(((long long)n_tokens * H + 7) / 8), 256, 0, s>>>(a);
+    MLC_LAUNCH_CHECK();
     if (ni <= 4) e = launch_delta_rule<4>(a, grid, s);
     else if (ni <= 8) e = launch_delta_rule<8>(a, grid, s);
     else if (ni <= 12) e = launch_delta_rule<12>(a, grid, s);

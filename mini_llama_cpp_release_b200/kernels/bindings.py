@@ -94,7 +94,7 @@ def core() -> ctypes.CDLL:
             "mlc_qk_norm_rope_cache": [P, LL, I, I, I, P, P, F, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P, P, LL, I, I, I, P],
             "mlc_softcap": [P, LL, F, P],
             "mlc_causal_conv": [P, LL, P, P, P, I, I, I, P, LL, P, P, P, I, I, I, P, LL, P],
-            "mlc_gated_delta_rule": [P, LL, I, I, I, P, LL, I, I, P, P, P, P, LL, P, P, I, I, I, I, I, I, P, P],
+            "mlc_gated_delta_rule": [P, LL, I, I, I, P, LL, I, I, P, P, P, P, LL, P, P, I, I, I, I, I, I, I, P, P],
             "mlc_gated_rmsnorm": [P, P, LL, P, F, LL, I, I, P, I, P],
             "mlc_block_gates": [P, P, P, P, P, P, I, I, I, F, P, P, P],
             "mlc_linear_scan": [P, P, P, LL, P, P, LL, P, P, I, I, I, F, P, I, P],
@@ -447,11 +447,12 @@ def gated_delta_rule(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
     n = qkv.shape[0]
     assert A_log.dtype == dt_bias.dtype == out.dtype == torch.float32
     assert state.shape[1] == heads * dim * vdim and out.shape == (n, heads * vdim)
-    coef = torch.empty(n * heads * 5, dtype=torch.float32, device=out.device)     # per (token, head): decay, step size, norms
+    # per (token, head): decay, step size, norms and, where tokens are taken four at a time, their products among themselves
+    coef = torch.empty((n + 3 * step.n_seqs) * heads * 16, dtype=torch.float32, device=out.device)
     _check(core().mlc_gated_delta_rule(_columns(qkv, 0), qkv.stride(0), q_col, k_col, v_col, _columns(gates, 0),
                                        gates.stride(0), b_col, a_col, A_log.data_ptr(), dt_bias.data_ptr(), coef.data_ptr(),
                                        state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(),
-                                       step.n_seqs, n, heads, kv_heads, dim, vdim, out.data_ptr(), _stream()),
+                                       step.n_seqs, n, step.max_q_len, heads, kv_heads, dim, vdim, out.data_ptr(), _stream()),
            "gated delta rule")
     count_launches(1)
 
