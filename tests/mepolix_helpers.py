@@ -76,7 +76,35 @@ ONLY_PARALLEL = {"architecture": "Mepolix", "vocab": 200, "width": 64, "logit_so
                              "mixer": parallel({"heads": 6, "kv_heads": 3, "dim": 48, "vdim": 32, "scale": 0.17, "rot": rot(24, 300.0, YARN)},
                                                {"width": 72, "blocks": 2, "conv": 5}, 0.9, 1.4)}]}
 
-CONFIGS = {"mixed": MIXED, "wide": WIDE, "tall": TALL, "delta": ONLY_DELTA, "parallel": ONLY_PARALLEL}
+# sizes the fast paths do not take: a width that is no multiple of 8 (the library's product), 200-entry keys (one token a
+# round), value heads of 36 (no 16-byte copies), nine taps (the plain convolution), a head that is not rotated at all,
+# value heads wider than key heads, gate blocks of 20, one tap, a delta layer that runs another's weights again
+ODD_A = {
+    "architecture": "Mepolix", "vocab": 77, "width": 100, "logit_softcap": 8.0, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "delta", "mlp": {"kind": "dense", "ff": 36}, "mixer": delta(2, 1, 200, 36, 9)},
+        {"type": "parallel", "mlp": None,
+         "mixer": parallel({"heads": 3, "kv_heads": 3, "dim": 24, "vdim": 40, "scale": 0.4, "rot": rot(0, 10000.0)},
+                           {"width": 60, "blocks": 3, "conv": 1}, 0.5, 2.0)},
+        {"type": "delta", "mlp": {"kind": "dense", "ff": 36}, "mixer": delta(2, 1, 200, 36, 9), "weights_of": 0},
+    ],
+}
+# two attention layers of different shapes (two cache groups; one with 128-entry value heads on 64-entry keys), eight
+# delta heads of 8 x 8, eight taps, no soft cap
+ODD_B = {
+    "architecture": "Mepolix", "vocab": 150, "width": 64, "logit_softcap": None, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": 48},
+         "mixer": parallel({"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 16, "scale": 0.25, "rot": rot(16, 777.0)},
+                           {"width": 128, "blocks": 4, "conv": 2}, 1.0, 1.0)},
+        {"type": "delta", "mlp": None, "mixer": delta(8, 8, 8, 8, 2)},
+        {"type": "parallel", "mlp": None,
+         "mixer": parallel({"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 128, "scale": 0.11, "rot": rot(32, 1e5, YARN)},
+                           {"width": 32, "blocks": 1, "conv": 8}, -0.8, 0.6)},
+    ],
+}
+
+CONFIGS = {"mixed": MIXED, "wide": WIDE, "tall": TALL, "delta": ONLY_DELTA, "parallel": ONLY_PARALLEL, "odd_a": ODD_A, "odd_b": ODD_B}
 
 
 def shape_weights(weights: Dict[str, torch.Tensor], seed: int) -> None:

@@ -60,6 +60,21 @@ def test_the_first_tokens_of_a_sequence(dtype):
             check(run_in_portions(ctx, tokens, [n]), oracle_logits(folder, tokens), dtype, f"{name} first {n}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["odd_a", "odd_b"])
+def test_sizes_that_the_fast_paths_do_not_take(name, dtype):
+    """A prompt, a portion of several tokens, and single tokens, for configurations whose sizes fall outside every
+    fast path (see mepolix_helpers.ODD_A, ODD_B)."""
+    folder = folder_of(name)
+    ctx = helpers.engine(folder, dtype).context
+    n = 110
+    tokens = random_tokens(n, vocab_of(name), 17)
+    want = oracle_logits(folder, tokens)
+    check(run_in_portions(ctx, tokens, [n]), want, dtype, f"{name} whole", many=True)
+    check(run_in_portions(ctx, tokens, [70, 77] + list(range(78, n + 1))), want, dtype, f"{name} in portions", many=True)
+    ctx.cache.check()
+
+
 # ------------------------------------------------------------------ decoding, portions
 
 @pytest.mark.parametrize("dtype", DTYPES)
