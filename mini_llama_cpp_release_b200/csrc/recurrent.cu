@@ -719,7 +719,9 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
 
 // ------------------------------------------------------------------ gates of the diagonal recurrence
 // The channels are cut into B blocks of bw; in block b: r = sigmoid(Wr[b]·u_b + br), i = sigmoid(Wi[b]·u_b + bi),
-// then per channel a = exp(-c·r·softplus(lam)) and drive = sqrt(1 - a²)·i·u.  Both products are float32
+// then per channel a = exp(-c·r·softplus(lam)) and drive = sqrt(1 - a²)·i·u.  What is stored is a - 1 = expm1(log a):
+// slow channels have a within 1e-5 of one, where a float32 a is a decay that is wrong by up to a percent of 1 - a, and
+// any bias of the exponential's last bit adds up over thousands of tokens; a - 1 keeps its digits.  Both products are float32
 // multiply-adds, each output one accumulator over ascending k, so a token's gates do not depend on the batch.
 // Tiles of 64 tokens x 64 channels, 4 x 4 per thread and gate.
 struct GateArgs {
@@ -729,7 +731,7 @@ struct GateArgs {
     const float* br;            // [W]
     const float* bi;            // [W]
     const float* lam;           // [W]
-    float* a_out;               // [n][W]
+    float* a_out;               // [n][W]: a - 1
     float* drive_out;           // [n][W]
     int n, W, bw;
     float c;
@@ -794,7 +796,7 @@ block_gates_kernel(GateArgs a) {
             const float gi = sigmoid_f(ai[i][j] + a.bi[ch]);
             const float log_a = -a.c * r * softplus_f(a.lam[ch]);
             const long long at = (long long)tok * a.W + ch;
-            a.a_out[at] = expf(log_a);
+            a.a_out[at] = expm1f(log_a);                  // a - 1: see the recurrence below
             // 1 - a² = -expm1(2 log a): formed from the logarithm, it keeps its digits where a is close to one
             a.drive_out[at] = sqrtf(-expm1f(2.0f * log_a)) * gi * a.u[at];
         }
@@ -802,8 +804,9 @@ block_gates_kernel(GateArgs a) {
 }
 
 // ------------------------------------------------------------------ the diagonal recurrence itself
-// S_t = a_t·S_{t-1} + drive_t per channel; out_t = S_t · gelu_tanh(y_t + y_bias) · out_scale.  A thread per
-// (sequence, channel) walks the sequence's tokens; the loads of four tokens are issued together.
+// S_t = a_t·S_{t-1} + drive_t per channel, formed as S + (a_t - 1)·S + drive_t from the stored a - 1;
+// out_t = S_t · gelu_tanh(y_t + y_bias) · out_scale.  A thread per (sequence, channel) walks the sequence's tokens;
+// the loads of four tokens are issued together.
 template <typename T>
 __global__ void linear_scan_kernel(const float* __restrict__ av, const float* __restrict__ drive, const float* __restrict__ y,
                                    long long y_stride, const float* __restrict__ y_bias, float* state, long long state_stride,
@@ -827,12 +830,12 @@ __global__ void linear_scan_kernel(const float* __restrict__ av, const float* __
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            S = fmaf(a4[e], S, d4[e]);
+            S = fmaf(a4[e], S, S) + d4[e];
             out[(long long)(t + e) * W + c] = from_float<T>(S * gelu_tanh_f(y4[e] + yb) * out_scale);
         }
     }
     for (; t < last; ++t) {
-        S = fmaf(av[(long long)t * W + c], S, drive[(long long)t * W + c]);
+        S = fmaf(av[(long long)t * W + c], S, S) + drive[(long long)t * W + c];
         out[(long long)t * W + c] = from_float<T>(S * gelu_tanh_f(y[(long long)t * y_stride + c] + yb) * out_scale);
     }
     *st = S;
@@ -870,14 +873,14 @@ linear_scan_long_kernel(const float* __restrict__ av, const float* __restrict__ 
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                A *= a8[e];
-                D = fmaf(a8[e], D, d8[e]);
+                A = fmaf(a8[e], A, A);
+                D = fmaf(a8[e], D, D) + d8[e];
             }
         }
         for (; t < hi; ++t) {
             const float at = av[(long long)t * W + c];
-            A *= at;
-            D = fmaf(at, D, drive[(long long)t * W + c]);
+            A = fmaf(at, A, A);
+            D = fmaf(at, D, D) + drive[(long long)t * W + c];
         }
     }
     As[warp][lane] = A;
@@ -899,12 +902,12 @@ linear_scan_long_kernel(const float* __restrict__ av, const float* __restrict__ 
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            S = fmaf(a8[e], S, d8[e]);
+            S = fmaf(a8[e], S, S) + d8[e];
             out[(long long)(t + e) * W + c] = from_float<T>(S * gelu_tanh_f(y8[e] + yb) * out_scale);
         }
     }
     for (; t < hi; ++t) {
-        S = fmaf(av[(long long)t * W + c], S, drive[(long long)t * W + c]);
+        S = fmaf(av[(long long)t * W + c], S, S) + drive[(long long)t * W + c];
         out[(long long)t * W + c] = from_float<T>(S * gelu_tanh_f(y[(long long)t * y_stride + c] + yb) * out_scale);
     }
     if (warp == SC_WARPS - 1) *st = S;
@@ -975,7 +978,8 @@ gates_scan_step_kernel(const float* __restrict__ u, const float* __restrict__ wr
     const float log_a = -c * r * softplus_f(lam[ch]);
     const float drive = sqrtf(-expm1f(2.0f * log_a)) * gi * us[sq * bw + oc];
     float* st = state + (long long)slots[token] * state_stride + ch;
-    const float S = fmaf(expf(log_a), *st, drive);
+    const float before = *st;
+    const float S = fmaf(expm1f(log_a), before, before) + drive;
     *st = S;
     const float yb = y_bias != nullptr ? y_bias[ch] : 0.0f;
     out[(long long)token * W + ch] = from_float<T>(S * gelu_tanh_f(y[(long long)token * y_stride + ch] + yb) * out_scale);

@@ -470,7 +470,8 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, gate_col: int, gain: torc
 def block_gates(u: torch.Tensor, w_r: torch.Tensor, w_i: torch.Tensor, b_r: torch.Tensor, b_i: torch.Tensor,
                 lam: torch.Tensor, c: float, a_out: torch.Tensor, drive_out: torch.Tensor) -> None:
     """Gates of the diagonal recurrence from u (float32 [n, W]) with block-diagonal weights [B, W/B, W/B]:
-    a = exp(-c · sigmoid(Wr u + br) · softplus(lam)), drive = sqrt(1 - a²) · sigmoid(Wi u + bi) · u."""
+    a = exp(-c · sigmoid(Wr u + br) · softplus(lam)), drive = sqrt(1 - a²) · sigmoid(Wi u + bi) · u.  `a_out` receives
+    a - 1 (as expm1 of the logarithm), which is what `linear_scan` takes."""
     require_cuda(u, w_r, w_i, b_r, b_i, lam, a_out, drive_out)
     n, W = u.shape
     B = w_r.shape[0]
@@ -484,7 +485,7 @@ def block_gates(u: torch.Tensor, w_r: torch.Tensor, w_i: torch.Tensor, b_r: torc
 def linear_scan(a: torch.Tensor, drive: torch.Tensor, y: torch.Tensor, y_col: int, y_bias: Optional[torch.Tensor],
                 state: torch.Tensor, step, out_scale: float, out: torch.Tensor) -> None:
     """S_t = a_t · S_{t-1} + drive_t per channel from each sequence's `state` (float32 [slots, W], left at the last
-    token's value); out = S · gelu_tanh(y[:, y_col:y_col+W] + y_bias) · out_scale."""
+    token's value), `a` holding a_t - 1; out = S · gelu_tanh(y[:, y_col:y_col+W] + y_bias) · out_scale."""
     require_cuda(a, drive, y_bias, out)
     _require_rows(state)
     n, W = a.shape
