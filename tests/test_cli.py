@@ -107,8 +107,9 @@ def test_model_comes_from_a_folder_a_file_or_a_random_configuration(tmp_path, mo
     helpers.ml.ModelConfig.from_dict(helpers.TINY_B).save(str(tmp_path / "mine"))
     folder_b, _ = cli.resolve_model(parse("--random", str(tmp_path / "mine" / "config.json")))
     assert helpers.ml.ModelConfig.from_folder(folder_b).vocab_size == 1000
-    # the five presets are the five configurations the measurements are quoted on
-    assert sorted(measure.PRESETS) == ["qwen2-0.5b", "qwen2-1.5b", "qwen2-7b", "tiny-a", "tiny-b"]
+    # the presets are the configurations the measurements are quoted on
+    assert sorted(measure.PRESETS) == ["mepolix-w1536", "mepolix-w3584", "mepolix-w896", "qwen2-0.5b", "qwen2-1.5b", "qwen2-7b",
+                                       "tiny-a", "tiny-b"]
     for raw in measure.PRESETS.values():
         helpers.ml.ModelConfig.from_dict(raw)
     # the engine's sizes
@@ -174,7 +175,11 @@ def test_the_kernel_timing_tool_reads_its_arguments():
     a = ap.parse_args("norm --tokens 8 --k 896 --slices 19".split())
     assert a.slices == 19
     assert ap.parse_args("attention --seqs 8 --context 4096 --cluster --phases --copies 8".split()).phases
-    for bad in (["conv"], ["gemm", "--epilogue", "relu"], ["attention", "--impl", "library"]):
+    a = ap.parse_args("delta --tokens 2048 --seqs 1 --heads 12 --kv-heads 6 --head-dim 128 --copies 4".split())
+    assert (a.kernel, a.tokens, a.seqs, a.heads, a.kv_heads, a.head_dim) == ("delta", 2048, 1, 12, 6, 128)
+    a = ap.parse_args("conv --tokens 8 --seqs 8 --k 3072 --taps 4".split())
+    assert (a.kernel, a.k, a.taps) == ("conv", 3072, 4)
+    for bad in (["pool"], ["gemm", "--epilogue", "relu"], ["attention", "--impl", "library"]):
         with pytest.raises(SystemExit):
             ap.parse_args(bad)
     root = os.path.join(ROOT, "profiles")
