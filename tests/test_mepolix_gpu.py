@@ -122,8 +122,9 @@ def test_keys_far_back_and_at_page_borders_in_prompts_and_in_decoding(dtype):
 
 
 def test_a_far_key_decides_the_logits():
-    """Weights made so that one key far back carries the answer: the query of the last token and the key of token 5 are
-    scaled up, so that the softmax picks that key out of 400; a kernel that lost it could not pass."""
+    """Weights made so that single keys carry the answer: the query and key matrices are six times larger, which makes
+    the scores thirty-six times larger and the softmax of every row a choice of one or two keys, wherever in the 400
+    they lie; a kernel that lost a far key, or a page's edge, would miss whole rows."""
     from safetensors.torch import load_file, save_file
     import os
     base = folder_of("parallel", seed=5)
@@ -139,7 +140,6 @@ def test_a_far_key_decides_the_logits():
     tokens = random_tokens(400, vocab_of("parallel"), 61)
     cfg, w = mh.oracle(folder)
     want = pm.forward(cfg, w, tokens).float()
-    # the plain attention's weights are peaked: the largest weight of the last rows is far from uniform
     for dtype in DTYPES:
         ctx = helpers.engine(folder, dtype).context
         check(run_in_portions(ctx, tokens, [390] + list(range(391, 401))), want, dtype, "far key")
