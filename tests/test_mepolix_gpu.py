@@ -122,9 +122,10 @@ def test_keys_far_back_and_at_page_borders_in_prompts_and_in_decoding(dtype):
 
 
 def test_a_far_key_decides_the_logits():
-    """Weights made so that single keys carry the answer: the query and key matrices are six times larger, which makes
-    the scores thirty-six times larger and the softmax of every row a choice of one or two keys, wherever in the 400
-    they lie; a kernel that lost a far key, or a page's edge, would miss whole rows."""
+    """Weights made so that single keys carry the answer: the gains of the query and key norms are four times larger
+    (the matrices themselves would be normalised away), which makes the scores sixteen times larger and the softmax of
+    every row a choice of one or two keys, wherever in the 400 they lie; a kernel that lost a far key, or a page's edge,
+    would miss whole rows."""
     from safetensors.torch import load_file, save_file
     import os
     base = folder_of("parallel", seed=5)
@@ -132,14 +133,22 @@ def test_a_far_key_decides_the_logits():
     if not os.path.isdir(folder):
         os.makedirs(folder)
         w = load_file(os.path.join(base, "model.safetensors"))
-        w["l0.mix.left.q"] = (w["l0.mix.left.q"].float() * 6.0).to(torch.bfloat16)
-        w["l0.mix.left.k"] = (w["l0.mix.left.k"].float() * 6.0).to(torch.bfloat16)
+        w["l0.mix.left.q.norm"] = (w["l0.mix.left.q.norm"].float() * 4.0).to(torch.bfloat16)
+        w["l0.mix.left.k.norm"] = (w["l0.mix.left.k.norm"].float() * 4.0).to(torch.bfloat16)
         save_file(w, os.path.join(folder, "model.safetensors"))
         with open(os.path.join(base, "config.json")) as f, open(os.path.join(folder, "config.json"), "w") as g:
             g.write(f.read())
     tokens = random_tokens(400, vocab_of("parallel"), 61)
     cfg, w = mh.oracle(folder)
     want = pm.forward(cfg, w, tokens).float()
+    # the plain attention is as peaked as claimed: in most rows the largest weight is above one half
+    h = w["embed"][torch.as_tensor(tokens)]
+    m = cfg["layers"][0]["mixer"]["left"]
+    q = pm.rotate(pm.rms_norm((h @ w["l0.mix.left.q"].t()).view(400, m["heads"], m["dim"]), w["l0.mix.left.q.norm"], 1e-5), torch.arange(400), m["rot"])
+    k = pm.rotate(pm.rms_norm((h @ w["l0.mix.left.k"].t()).view(400, m["kv_heads"], m["dim"]), w["l0.mix.left.k.norm"], 1e-5), torch.arange(400), m["rot"])
+    s0 = (q[:, 0] @ k[:, 0].t()) * m["scale"]
+    s0 = s0.masked_fill(torch.arange(400)[:, None] < torch.arange(400)[None, :], float("-inf"))
+    assert float((torch.softmax(s0, dim=-1).max(dim=-1).values[100:] > 0.5).float().mean()) > 0.5
     for dtype in DTYPES:
         ctx = helpers.engine(folder, dtype).context
         check(run_in_portions(ctx, tokens, [390] + list(range(391, 401))), want, dtype, "far key")
