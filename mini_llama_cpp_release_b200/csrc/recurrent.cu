@@ -45,21 +45,23 @@ struct ConvArgs {
 
 __device__ __forceinline__ float conv_finish(float acc, int act) { return act == 1 ? acc * sigmoid_f(acc) : acc; }
 
-// A block takes CONV_TOKENS consecutive tokens x 256 channels.  Where each token stands in its sequence is looked up
+// A block takes CONV_SUB tiles of CONV_TOKENS consecutive tokens x 256 channels, one after the other.  Where each token stands in its sequence is looked up
 // once per block; the tile's inputs, with the taps-1 rows before it, are loaded in one sweep of independent loads into
 // shared memory (a thread reads back only what it wrote itself); only a sequence's first taps-1 tokens reach for the
 // state.  CONV_MAX_TAPS bounds the rows kept; longer filters take the plain kernel below.
 constexpr int CONV_TOKENS = 16;
 constexpr int CONV_MAX_TAPS = 8;
+constexpr int CONV_SUB = 1;          // tiles a block walks one after the other (more than one was slower: 30 against 26 us
+                                     // for 2,048 tokens x 3,072 channels; the kernel waits on latency, not on its look-up)
 
 __global__ void __launch_bounds__(256)
 conv_out_kernel(ConvArgs a) {
-    __shared__ int t_of[CONV_TOKENS];
-    __shared__ long long state_of[CONV_TOKENS];
+    __shared__ int t_of[CONV_SUB * CONV_TOKENS];
+    __shared__ long long state_of[CONV_SUB * CONV_TOKENS];
     __shared__ float tile[CONV_TOKENS + CONV_MAX_TAPS - 1][256];
-    const int tok0 = blockIdx.x * CONV_TOKENS, c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (threadIdx.x < CONV_TOKENS) {
-        const int token = tok0 + threadIdx.x;
+    const int block_tok0 = blockIdx.x * CONV_SUB * CONV_TOKENS, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (threadIdx.x < CONV_SUB * CONV_TOKENS) {
+        const int token = block_tok0 + threadIdx.x;
         if (token < a.n_tokens) {
             const int seq = a.tok_seq[token];
             t_of[threadIdx.x] = token - a.cu_seqlens[seq];
@@ -70,35 +72,39 @@ conv_out_kernel(ConvArgs a) {
     if (c >= a.C) return;
     const int halo = a.taps - 1;
     const float ib = a.in_bias != nullptr ? a.in_bias[c] : 0.0f;
-    const int n_here = min(CONV_TOKENS, a.n_tokens - tok0);
-    float in[CONV_TOKENS + CONV_MAX_TAPS - 1];
-#pragma unroll
-    for (int r = 0; r < CONV_TOKENS + CONV_MAX_TAPS - 1; ++r) {      // every load of the tile in flight at once
-        const int token = tok0 - halo + r;
-        in[r] = (r < n_here + halo && token >= 0) ? a.x[(long long)token * a.x_stride + c] : 0.0f;
-    }
-#pragma unroll
-    for (int r = 0; r < CONV_TOKENS + CONV_MAX_TAPS - 1; ++r) tile[r][threadIdx.x] = in[r] + ib;
     float w[CONV_MAX_TAPS];
 #pragma unroll
     for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < a.taps ? a.w[(long long)c * a.taps + a.taps - 1 - j] : 0.0f;
     const float b0 = a.bias != nullptr ? a.bias[c] : 0.0f;
-    for (int i = 0; i < n_here; ++i) {
-        const int t = t_of[i];
-        float acc = b0;
-        if (t >= halo) {
+    for (int sub = 0; sub < CONV_SUB; ++sub) {
+        const int tok0 = block_tok0 + sub * CONV_TOKENS;
+        if (tok0 >= a.n_tokens) break;
+        const int n_here = min(CONV_TOKENS, a.n_tokens - tok0);
+        float in[CONV_TOKENS + CONV_MAX_TAPS - 1];
 #pragma unroll
-            for (int j = 0; j < CONV_MAX_TAPS; ++j)
-                if (j < a.taps) acc = fmaf(w[j], tile[i + halo - j][threadIdx.x], acc);
-        } else {
-            const float* st = a.state + state_of[i];
-            for (int j = 0; j < a.taps; ++j) {
-                const int src = t - j;
-                const float v = src >= 0 ? tile[i + halo - j][threadIdx.x] : st[(long long)(halo + src) * a.C + c];
-                acc = fmaf(a.w[(long long)c * a.taps + a.taps - 1 - j], v, acc);
-            }
+        for (int r = 0; r < CONV_TOKENS + CONV_MAX_TAPS - 1; ++r) {      // every load of the tile in flight at once
+            const int token = tok0 - halo + r;
+            in[r] = (r < n_here + halo && token >= 0) ? a.x[(long long)token * a.x_stride + c] : 0.0f;
         }
-        a.out[(long long)(tok0 + i) * a.out_stride + c] = conv_finish(acc, a.act);
+#pragma unroll
+        for (int r = 0; r < CONV_TOKENS + CONV_MAX_TAPS - 1; ++r) tile[r][threadIdx.x] = in[r] + ib;   // a column of one's own
+        for (int i = 0; i < n_here; ++i) {
+            const int t = t_of[sub * CONV_TOKENS + i];
+            float acc = b0;
+            if (t >= halo) {
+#pragma unroll
+                for (int j = 0; j < CONV_MAX_TAPS; ++j)
+                    if (j < a.taps) acc = fmaf(w[j], tile[i + halo - j][threadIdx.x], acc);
+            } else {
+                const float* st = a.state + state_of[sub * CONV_TOKENS + i];
+                for (int j = 0; j < a.taps; ++j) {
+                    const int src = t - j;
+                    const float v = src >= 0 ? tile[i + halo - j][threadIdx.x] : st[(long long)(halo + src) * a.C + c];
+                    acc = fmaf(a.w[(long long)c * a.taps + a.taps - 1 - j], v, acc);
+                }
+            }
+            a.out[(long long)(tok0 + i) * a.out_stride + c] = conv_finish(acc, a.act);
+        }
     }
 }
 
@@ -707,6 +713,27 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
     const int head = (int)(row % H);
     const float* src = o + row * vdim;
     const float* g = gate + token * gate_stride + (long long)head * vdim;
+    if (vdim <= 256) {                              // the row, its gates and gains in registers: every load issued at once
+        float v[8], z[8], wv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int d = lane + 32 * k;
+            v[k] = d < vdim ? src[d] : 0.0f;
+            z[k] = d < vdim ? g[d] : 0.0f;
+            wv[k] = d < vdim ? w[d] : 0.0f;
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
+        ss = warp_sum(ss);
+        const float f = 1.0f / sqrtf(ss / (float)vdim + eps);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int d = lane + 32 * k;
+            if (d < vdim) out[row * vdim + d] = from_float<T>(v[k] * f * wv[k] * (z[k] * sigmoid_f(z[k])));
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int d = lane; d < vdim; d += 32) ss += src[d] * src[d];
     ss = warp_sum(ss);
@@ -841,12 +868,12 @@ __global__ void linear_scan_kernel(const float* __restrict__ av, const float* __
     *st = S;
 }
 
-// The same for long runs of tokens: 32 channels (a lane each) and SC_WARPS warps per block, the sequence's new tokens
+// The same for long runs of tokens: 32 channels (a lane each) and SC_WARPS warps (1,024 threads) per block, the sequence's new tokens
 // cut into SC_WARPS consecutive segments.  A warp first folds its segment into the pair (A, D) with
 // S_end = A·S_begin + D; the pairs of the segments before it, applied in order to the sequence's state, give the
 // state its segment starts from; then it walks its segment token by token as above.  Eight tokens' loads are issued
 // together in both passes.
-constexpr int SC_WARPS = 16;
+constexpr int SC_WARPS = 32;
 
 template <typename T>
 __global__ void __launch_bounds__(SC_WARPS * 32)
@@ -1007,7 +1034,7 @@ extern "C" int mlc_causal_conv(const float* x, long long x_stride, const float* 
     }
     if ((C + 255) / 256 > 65535) return MLC_ERR_BAD_SIZE;
     if (taps <= CONV_MAX_TAPS)
-        conv_out_kernel<<<dim3((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + 255) / 256), 256, 0, s>>>(a);
+        conv_out_kernel<<<dim3((n_tokens + CONV_SUB * CONV_TOKENS - 1) / (CONV_SUB * CONV_TOKENS), (C + 255) / 256), 256, 0, s>>>(a);
     else
         conv_out_plain_kernel<<<dim3(n_tokens, (C + 255) / 256), 256, 0, s>>>(a);
     MLC_LAUNCH_CHECK();

@@ -350,7 +350,7 @@ def test_gated_delta_rule_kernel_against_a_loop(H, G, dim, vdim):
 @pytest.mark.parametrize("W, B", [(96, 3), (64, 1), (40, 5), (200, 2)])
 def test_recurrence_gates_and_scan_against_a_loop(W, B):
     g = torch.Generator().manual_seed(W)
-    lens, slots = [30, 1, 70], [2, 0, 1]
+    lens, slots = [30, 1, 170], [2, 0, 1]              # the longest run takes the kernel that scans segments side by side
     n, bw = sum(lens), W // B
     u = torch.randn(n, W, generator=g)
     wr, wi = torch.randn(B, bw, bw, generator=g) * 0.3, torch.randn(B, bw, bw, generator=g) * 0.3
