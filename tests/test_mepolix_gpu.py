@@ -422,3 +422,19 @@ def test_one_token_form_of_gates_and_recurrence(W, B, n_seqs):
     assert torch.allclose(out.cpu().double(), S * pm.gelu_tanh(y[:, 2:2 + W].double() + yb.double()) * 1.25, atol=1e-5, rtol=1e-4)
     untouched = [s for s in range(n_seqs + 2) if s not in slots]
     assert torch.equal(dev_state[untouched].cpu(), state[untouched])
+
+
+def test_the_rotation_table_grows_with_the_sequence(monkeypatch):
+    """The model names no largest position: the table of cosines and sines is rebuilt, twice as long, whenever a step
+    reaches beyond it.  With a table that starts at 64 positions a 300-token sequence makes it grow three times, in a
+    prompt, in a portion and in single-token steps; the logits stay the plain implementation's."""
+    import mini_llama_cpp_release_b200 as ml
+    from mini_llama_cpp_release_b200.parts.rotary import RopePartial
+    monkeypatch.setattr(RopePartial, "MIN_POSITIONS", 64)
+    folder = folder_of("mixed")
+    llm = ml.load(folder, dtype="float32", max_tokens=1024)
+    tokens = random_tokens(300, vocab_of("mixed"), 131)
+    got = run_in_portions(llm.context, tokens, [50, 120] + list(range(121, 135)) + [300])
+    check(got, oracle_logits(folder, tokens), "float32", "growing table")
+    rope = llm.model.parts.blocks[0].mixer.left.position
+    assert rope.table.shape[0] == 512 and len(rope._old) == 3
