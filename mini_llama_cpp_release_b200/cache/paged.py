@@ -79,7 +79,7 @@ def cache_bytes_per_token(needs: Sequence[Optional[CacheNeed]], reads_cache_of: 
     """Key and value bytes one token of one sequence occupies over all groups, for elements of `itemsize` bytes
     (a window group holds at most its window of them)."""
     groups, _ = plan_groups(needs, reads_cache_of)
-    return sum(2 * len(g.entries) * g.need.kv_heads * g.need.head_dim * itemsize for g in groups)
+    return sum((1 if g.need.shared_kv else 2) * len(g.entries) * g.need.kv_heads * g.need.head_dim * itemsize for g in groups)
 
 
 class SlotBook:
@@ -176,7 +176,8 @@ class SlotBook:
             if layout.need.kind == "window" and w:
                 first_needed = max(0, L - w + 1)                 # the next token reads keys from here on
                 plist = self.page_lists[slot][g]
-                for i in range(min(len(plist), first_needed // self.page_size)):
+                kept = (layout.need.keep_first + self.page_size - 1) // self.page_size   # pages of first keys that stay visible
+                for i in range(kept, min(len(plist), first_needed // self.page_size)):
                     if plist[i] >= 0:
                         self.pages[g].give_back(plist[i])
                         plist[i] = -1
@@ -215,7 +216,8 @@ class PagedCache(SlotBook):
         for layout in groups:
             shape = (len(layout.entries), self.n_pages, layout.need.kv_heads, page_size, layout.need.head_dim)
             self.k_pools.append(torch.empty(shape, dtype=dtype, device=device))
-            self.v_pools.append(torch.empty(shape, dtype=dtype, device=device))
+            # a group whose values are read out of its key rows has one pool under both names
+            self.v_pools.append(self.k_pools[-1] if layout.need.shared_kv else torch.empty(shape, dtype=dtype, device=device))
         self.state: List[Optional[torch.Tensor]] = [
             torch.zeros((self.max_seqs, *s.shape), dtype=s.dtype, device=device) if s is not None else None
             for s in states]
@@ -242,13 +244,14 @@ class PagedCache(SlotBook):
                 s.index_copy_(0, slots_long, rows)
 
     def bytes(self) -> int:
-        n = sum(t.numel() * t.element_size() for t in self.k_pools + self.v_pools)
+        n = sum(t.numel() * t.element_size() for t in self.k_pools)
+        n += sum(v.numel() * v.element_size() for k, v in zip(self.k_pools, self.v_pools) if v is not k)
         return n + sum(s.numel() * s.element_size() for s in self.state if s is not None)
 
     def bytes_per_token(self) -> int:
         """Key and value bytes one token of one sequence occupies over all groups."""
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.need.kv_heads * g.need.head_dim * item for g in self.groups)
+        return sum((1 if g.need.shared_kv else 2) * len(g.entries) * g.need.kv_heads * g.need.head_dim * item for g in self.groups)
 
     def view(self, entry: int, page_tables: Sequence[torch.Tensor]) -> Optional[KVView]:
         """The cache of schedule entry `entry` for the sequences whose page lists (one tensor

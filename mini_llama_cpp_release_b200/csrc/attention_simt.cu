@@ -5,7 +5,8 @@
 // One kernel serves prompts, continuation chunks and single decoded tokens: a step gives
 // each sequence q_len new tokens at positions start_pos .. start_pos + q_len - 1, their
 // keys and values are already in the cache, and a token at position p reads keys
-// lo(p) .. p, with lo(p) = 0 or p - window + 1.  The reference computes the same thing
+// lo(p) .. p, with lo(p) = 0 or p - window + 1, and beside a window the first `keep_first`
+// keys of the sequence, which stay visible at any distance (at their true positions).  The reference computes the same thing
 // one (head, position) at a time: score = (q·k)·1/sqrt(hd), max, exp, sum, weighted sum
 // of values (src/forward.cpp:585-611; src/ops.cpp:43-70); query head h reads kv head
 // h / (H/KV) (src/forward.cpp:524-526).  Here a block holds up to 16 (token, head) rows
@@ -35,6 +36,7 @@ struct AttnArgs {
     int q_heads;
     int group;                // query heads per kv head
     int window;               // 0: all keys
+    int keep_first;           // with a window: keys at positions below this stay visible whatever the distance
     int tokens_per_block;     // TQ
     int heads_per_block;      // GH, TQ*GH <= 16
     int head_chunks;          // ceil(group / GH)
@@ -82,9 +84,14 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / ATT_TILE, tile_end = p_last / ATT_TILE + 1;
-    const int per_split = (tile_end - tile_begin + a.n_splits - 1) / a.n_splits;
-    const int my_begin = tile_begin + split * per_split;
-    const int my_end = min(tile_end, my_begin + per_split);
+    // tiles of kept first keys that lie before the window's first tile are walked ahead of it: the walk's tile number
+    // v stands for tile v below `head_tiles`, and for tile_begin + (v - head_tiles) from there on
+    const int keep = (a.window > 0) ? a.keep_first : 0;
+    const int head_tiles = min(tile_begin, (keep + ATT_TILE - 1) / ATT_TILE);
+    const int walk = head_tiles + tile_end - tile_begin;
+    const int per_split = (walk + a.n_splits - 1) / a.n_splits;
+    const int my_begin = split * per_split;
+    const int my_end = min(walk, my_begin + per_split);
 
     float m[ATT_ROWS_PER_WARP], l[ATT_ROWS_PER_WARP], acc[ATT_ROWS_PER_WARP][ATT_ACC];
     int row_lo[ATT_ROWS_PER_WARP], row_hi[ATT_ROWS_PER_WARP];
@@ -104,11 +111,12 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
 
     const T* kp = (const T*)c.k_pool;
     const T* vp = (const T*)c.v_pool;
-    for (int tile = my_begin; tile < my_end; ++tile) {
+    for (int v = my_begin; v < my_end; ++v) {
+        const int tile = v < head_tiles ? v : tile_begin + (v - head_tiles);
         __syncthreads();   // previous tile's readers are done (and Qs is staged)
         if (threadIdx.x < ATT_TILE) {
             const int kpos = tile * ATT_TILE + threadIdx.x;
-            key_off[threadIdx.x] = (kpos >= lo_block && kpos <= p_last) ? paged_offset(c, b, kpos, kvh) : -1;
+            key_off[threadIdx.x] = ((kpos >= lo_block || kpos < keep) && kpos <= p_last) ? paged_offset(c, b, kpos, kvh) : -1;
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < ATT_TILE * hd; idx += blockDim.x) {
@@ -128,7 +136,7 @@ attention_simt_kernel(AttnArgs a, PagedKV c) {
 #pragma unroll
         for (int i = 0; i < ATT_ROWS_PER_WARP; ++i) {
             if (!row_ok[i]) continue;
-            const bool in_range = kpos >= row_lo[i] && kpos <= row_hi[i];
+            const bool in_range = (kpos >= row_lo[i] || kpos < keep) && kpos <= row_hi[i];
             float s = -INFINITY;
             if (in_range) {
                 const float* qr = Qs + (warp * ATT_ROWS_PER_WARP + i) * hd;
@@ -237,7 +245,7 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
                                  int n_seqs, int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
                                  int window, int n_splits, float* part_ml, float* part_o, void* k_pool, void* v_pool,
                                  const int* page_table, long long entry_offset, int pages_per_seq, int page_size,
-                                 cudaStream_t s, const float* sinks = nullptr) {
+                                 cudaStream_t s, const float* sinks = nullptr, int keep_first = 0) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd <= 0 || hd > ATT_MAX_HD || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return MLC_ERR_BAD_SIZE;
     if (n_splits < 1 || (n_splits > 1 && (part_ml == nullptr || part_o == nullptr))) return MLC_ERR_BAD_SIZE;
@@ -255,6 +263,7 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
     a.q_heads = q_heads;
     a.group = q_heads / kv_heads;
     a.window = window;
+    a.keep_first = keep_first < 0 ? 0 : keep_first;
     a.heads_per_block = a.group < ATT_ROWS ? a.group : ATT_ROWS;
     a.tokens_per_block = ATT_ROWS / a.heads_per_block;
     a.head_chunks = (a.group + a.heads_per_block - 1) / a.heads_per_block;
@@ -309,10 +318,11 @@ extern "C" int mlc_attention_simt(const void* q, void* out, int dtype, const int
                                   const int* start_pos, int n_seqs, int n_tokens, int max_q_len, int q_heads,
                                   int kv_heads, int hd, float scale, int window, int n_splits, float* part_ml,
                                   float* part_o, void* k_pool, void* v_pool, const int* page_table,
-                                  long long entry_offset, int pages_per_seq, int page_size, const float* sinks, void* stream) {
+                                  long long entry_offset, int pages_per_seq, int page_size, const float* sinks, int keep_first,
+                                  void* stream) {
     return launch_attention_simt(q, out, dtype, cu_seqlens, start_pos, n_seqs, n_tokens, max_q_len, q_heads, kv_heads, hd,
                                  scale, window, n_splits, part_ml, part_o, k_pool, v_pool, page_table, entry_offset,
-                                 pages_per_seq, page_size, (cudaStream_t)stream, sinks);
+                                 pages_per_seq, page_size, (cudaStream_t)stream, sinks, keep_first);
 }
 
 // Merge partial results that another attention kernel left in part_ml / part_o

@@ -1,0 +1,290 @@
+// Mixture of experts: routing, the plan that sorts a step's (token, expert) pairs by expert, the product of every
+// sorted row with its own expert's matrix, and the weighted sum back per token.
+//
+//   route      z = logits + bias (float32); the `top` largest of a token's E logits are chosen (the lower index wins a
+//              tie) and weighted by the softmax over the chosen logits only.
+//   plan       pairs (token, j-th choice) are ordered by expert, inside an expert by pair number; every expert's run
+//              starts on a multiple of `tile` rows, the rows between runs are padding (source token -1).  Nothing
+//              comes back to the host: the tables below are all a later kernel needs.
+//                 row_of[pair]      the pair's row in the sorted order
+//                 src_tok[row]      the token a row computes, -1 for padding
+//                 tile_expert[t]    the expert of rows [t*tile, (t+1)*tile), -1 past the last run
+//   grouped    out[row] = W[tile_expert[row / tile]] · x[src] with float32 accumulation, the K range walked in the
+//              same order for every row, so a token's result does not depend on what else is in the step.
+//   combine    y[token] = sum_j weight[token][j] · out[row_of[token][j]], j in the order of the choices.
+#include "common.cuh"
+
+namespace mlc {
+
+constexpr int ROUTE_MAX_PER_LANE = 8;          // E <= 256
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int n, int E, int top,
+                                 int* __restrict__ ids, float* __restrict__ weights) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n) return;
+    const int lane = threadIdx.x & 31;
+    float z[ROUTE_MAX_PER_LANE];
+#pragma unroll
+    for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+        const int e = lane + 32 * k;
+        z[k] = e < E ? logits[(long long)t * E + e] + (bias != nullptr ? bias[e] : 0.0f) : -INFINITY;
+    }
+    float mine = -INFINITY;          // lane j keeps the j-th chosen logit
+    float first = 0.0f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int where = 0x7fffffff;
+#pragma unroll
+        for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
+            const int e = lane + 32 * k;
+            if (e < E && (z[k] > best || (z[k] == best && e < where))) {
+                best = z[k];
+                where = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int ow = __shfl_xor_sync(0xffffffffu, where, o);
+            if (ob > best || (ob == best && ow < where)) {
+                best = ob;
+                where = ow;
+            }
+        }
+        if (where != 0x7fffffff && (where & 31) == lane) z[where >> 5] = -INFINITY;
+        if (lane == j) mine = best;
+        if (j == 0) first = best;                     // the largest: the softmax's reference point
+        if (lane == 0) ids[(long long)t * top + j] = where == 0x7fffffff ? 0 : where;
+    }
+    const float p = lane < top ? expf(mine - first) : 0.0f;
+    const float sum = warp_sum(p);
+    if (lane < top) weights[(long long)t * top + lane] = p / sum;
+}
+
+// One block.  Shared: counts and offsets per expert.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int top, int E, int tile, int max_rows, int* __restrict__ row_of,
+                int* __restrict__ src_tok, int* __restrict__ tile_expert) {
+    extern __shared__ int sh[];
+    int* cnt = sh;             // [E]
+    int* off = sh + E;         // [E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += n_warps) {
+        int c = 0;
+        for (int p = lane; p < n_pairs; p += 32) c += ids[p] == e;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) cnt[e] = c;
+    }
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_tok[r] = -1;
+    for (int t = threadIdx.x; t < max_rows / tile; t += blockDim.x) tile_expert[t] = -1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = at;
+            const int tiles = (cnt[e] + tile - 1) / tile;
+            for (int t = 0; t < tiles; ++t) tile_expert[at / tile + t] = e;
+            at += tiles * tile;
+        }
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += n_warps) {
+        int base = off[e];
+        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
+            const int p = p0 + lane;
+            const bool hit = p < n_pairs && ids[p] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int row = base + __popc(mask & ((1u << lane) - 1u));
+                row_of[p] = row;
+                src_tok[row] = p / top;
+            }
+            base += __popc(mask);
+        }
+    }
+}
+
+constexpr int GL_TILE = 64;        // rows and columns of a block's tile
+constexpr int GL_K = 16;
+
+// out[row][j] = sum_k x[src(row)][k] · W[expert][j][k].  W: [E][N][K].  A block: 64 rows x 64 columns, 256 threads,
+// a thread 4 x 4.  `tile` (rows per expert run granule) is a multiple of 64, so a block's rows share an expert.
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+grouped_linear_kernel(const TX* __restrict__ x, const int* __restrict__ src_tok, const TW* __restrict__ w,
+                      const int* __restrict__ tile_expert, int tile, int N, int K, TO* __restrict__ out) {
+    const int row0 = blockIdx.y * GL_TILE;
+    const int e = tile_expert[row0 / tile];
+    if (e < 0) return;
+    const int col0 = blockIdx.x * GL_TILE;
+    __shared__ float xs[GL_K][GL_TILE + 1];
+    __shared__ float ws[GL_K][GL_TILE + 1];
+    __shared__ int src[GL_TILE];
+    if (threadIdx.x < GL_TILE) src[threadIdx.x] = src_tok != nullptr ? src_tok[row0 + threadIdx.x] : row0 + threadIdx.x;
+    __syncthreads();
+    const TW* we = w + (long long)e * N * K;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += GL_K) {
+        for (int idx = threadIdx.x; idx < GL_TILE * GL_K; idx += 256) {
+            const int r = idx / GL_K, k = idx % GL_K;
+            const int s = src[r];
+            xs[k][r] = (s >= 0 && k0 + k < K) ? to_float(x[(long long)s * K + k0 + k]) : 0.0f;
+            const int c = col0 + r;
+            ws[k][r] = (c < N && k0 + k < K) ? to_float(we[(long long)c * K + k0 + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GL_K; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (src[r] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = col0 + tx * 4 + j;
+            if (c < N) out[(long long)(row0 + r) * N + c] = from_float<TO>(acc[i][j]);
+        }
+    }
+}
+
+// rows[r] = x[src_tok[r]] (zeros for padding), for products that want their operand dense
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ src_tok, int d, T* __restrict__ rows) {
+    const int r = blockIdx.x;
+    const int s = src_tok[r];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) rows[(long long)r * d + i] = s >= 0 ? x[(long long)s * d + i] : from_float<T>(0.0f);
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
+                                   int top, int d, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < top; ++j)
+            acc = fmaf(weights[(long long)t * top + j], y[(long long)row_of[(long long)t * top + j] * d + i], acc);
+        out[(long long)t * d + i] = acc;
+    }
+}
+
+// x[t][i] += s1[i] · sum_slices y1[.][t][i] (+ s2[i] · sum_slices y2[.][t][i]); a null factor is one
+__global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ y1, int slices1, const float* __restrict__ s1,
+                                  const float* __restrict__ y2, int slices2, const float* __restrict__ s2, long long total, int d) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = (int)(idx % d);
+    float a = 0.0f;
+    for (int s = 0; s < slices1; ++s) a += y1[(long long)s * total + idx];
+    float v = x[idx] + (s1 != nullptr ? s1[i] * a : a);
+    if (y2 != nullptr) {
+        float b = 0.0f;
+        for (int s = 0; s < slices2; ++s) b += y2[(long long)s * total + idx];
+        v += s2 != nullptr ? s2[i] * b : b;
+    }
+    x[idx] = v;
+}
+
+}  // namespace mlc
+
+using namespace mlc;
+
+extern "C" int mlc_moe_route(const float* logits, const float* bias, int n, int E, int top, int* ids, float* weights,
+                             void* stream) {
+    if (n <= 0) return 0;
+    if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > 32 || top > E) return MLC_ERR_BAD_SIZE;
+    moe_route_kernel<<<(n + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits, bias, n, E, top, ids, weights);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_moe_plan(const int* ids, int n_pairs, int top, int E, int tile, int max_rows, int* row_of, int* src_tok,
+                            int* tile_expert, void* stream) {
+    if (n_pairs <= 0) return 0;
+    if (E <= 0 || E > 4096 || tile <= 0 || max_rows % tile != 0 || top <= 0) return MLC_ERR_BAD_SIZE;
+    // every expert's run, rounded up to whole tiles, must fit
+    const long long most = (long long)n_pairs + (long long)(E < n_pairs ? E : n_pairs) * (tile - 1);     // only experts that were chosen have a run
+    if ((long long)max_rows < most - most % tile) return MLC_ERR_BAD_SIZE;
+    moe_plan_kernel<<<1, 1024, 2 * E * sizeof(int), (cudaStream_t)stream>>>(ids, n_pairs, top, E, tile, max_rows, row_of,
+                                                                            src_tok, tile_expert);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_grouped_linear(const void* x, int x_dtype, const int* src_tok, const void* w, int w_dtype,
+                                  const int* tile_expert, int tile, int max_rows, int N, int K, void* out, int out_dtype,
+                                  void* stream) {
+    if (max_rows <= 0) return 0;
+    if (tile % GL_TILE != 0 || max_rows % tile != 0 || N <= 0 || K <= 0) return MLC_ERR_BAD_SIZE;
+    const dim3 grid((N + GL_TILE - 1) / GL_TILE, max_rows / GL_TILE);
+    if (grid.y > 65535) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int code = x_dtype * 4 + w_dtype * 2 + out_dtype;
+#define MLC_GL(TX, TW, TO) \
+    grouped_linear_kernel<TX, TW, TO><<<grid, 256, 0, s>>>((const TX*)x, src_tok, (const TW*)w, tile_expert, tile, N, K, (TO*)out)
+    switch (code) {
+        case 0: MLC_GL(float, float, float); break;
+        case 1: MLC_GL(float, float, bf16); break;
+        case 2: MLC_GL(float, bf16, float); break;
+        case 3: MLC_GL(float, bf16, bf16); break;
+        case 4: MLC_GL(bf16, float, float); break;
+        case 5: MLC_GL(bf16, float, bf16); break;
+        case 6: MLC_GL(bf16, bf16, float); break;
+        case 7: MLC_GL(bf16, bf16, bf16); break;
+        default: return MLC_ERR_BAD_DTYPE;
+    }
+#undef MLC_GL
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_moe_gather(const void* x, int dtype, const int* src_tok, int max_rows, int d, void* rows, void* stream) {
+    if (max_rows <= 0) return 0;
+    if (d <= 0) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 256 ? 256 : 64;
+    if (dtype == MLC_DTYPE_F32)
+        moe_gather_kernel<float><<<max_rows, threads, 0, s>>>((const float*)x, src_tok, d, (float*)rows);
+    else if (dtype == MLC_DTYPE_BF16)
+        moe_gather_kernel<bf16><<<max_rows, threads, 0, s>>>((const bf16*)x, src_tok, d, (bf16*)rows);
+    else
+        return MLC_ERR_BAD_DTYPE;
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_moe_combine(const float* y, const int* row_of, const float* weights, int n, int top, int d, float* out,
+                               void* stream) {
+    if (n <= 0) return 0;
+    if (top <= 0 || d <= 0) return MLC_ERR_BAD_SIZE;
+    moe_combine_kernel<<<n, d >= 256 ? 256 : 64, 0, (cudaStream_t)stream>>>(y, row_of, weights, top, d, out);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_scaled_add(float* x, const float* y1, int slices1, const float* s1, const float* y2, int slices2,
+                              const float* s2, long long n, int d, void* stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || y1 == nullptr || slices1 < 1 || (y2 != nullptr && slices2 < 1)) return MLC_ERR_BAD_SIZE;
+    const long long total = n * d;
+    scaled_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, y1, slices1, s1, y2, slices2, s2,
+                                                                                         total, d);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}

@@ -52,6 +52,7 @@ class Model:
         self.parts = build_parts(spec)
         self.loaded = False
         self.load_summary = {}
+        self._keeps_embedding = any(getattr(b, "reads_embedding", False) for b in self.parts.blocks)
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -112,6 +113,9 @@ class Model:
         the step's keys, values and state go into `cache`."""
         rt = self.runtime
         x = self.parts.embedding.forward(step.tokens)
+        if self._keeps_embedding:
+            # a block reads the embedding's output later in the step; the stream itself is updated in place
+            step.handover["embedding_output"] = x.clone()
         pending: Optional[torch.Tensor] = None
         for k, entry in enumerate(self.spec.schedule):
             memory = MixerMemory(kv=cache.view(k, step.page_tables), state=cache.state[k],

@@ -17,6 +17,8 @@ __all__ = [
     "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "PinnedCopy", "decode_advance",
     "layernorm", "qk_norm_rope_cache", "softcap", "convert", "causal_conv", "gated_delta_rule", "gated_rmsnorm", "block_gates",
     "linear_scan", "gates_scan_step", "gates_scan_step_takes",
+    "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "gla", "latent_prepare",
+    "head_project",
 ]
 
 
@@ -103,7 +105,16 @@ def core() -> ctypes.CDLL:
             "mlc_silu_mul": [P, I, I, I, I, P, I, P],
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
-            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P, P],
+            "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P, I, P],
+            "mlc_moe_route": [P, P, I, I, I, P, P, P],
+            "mlc_moe_plan": [P, I, I, I, I, I, P, P, P, P],
+            "mlc_grouped_linear": [P, I, P, P, I, P, I, I, I, I, P, I, P],
+            "mlc_moe_gather": [P, I, P, I, I, P, P],
+            "mlc_moe_combine": [P, P, P, I, I, I, P, P],
+            "mlc_scaled_add": [P, P, I, P, P, I, P, LL, I, P],
+            "mlc_gla": [P, LL, I, I, I, P, P, F, P, LL, P, P, I, I, I, I, I, P, P],
+            "mlc_latent_prepare": [P, LL, I, I, P, F, P, P, P, I, I, I, I, I, I, I, P, I, I, P, P, LL, I, I, P],
+            "mlc_head_project": [P, I, LL, LL, P, I, LL, LL, LL, P, I, LL, LL, I, I, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P, LL, I, P],
             "mlc_attention_combine": [P, P, LL, I, I, P, I, P, I, P],
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
@@ -230,8 +241,9 @@ def qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.T
 def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                    n_seqs: int, max_q_len: int, q_heads: int, kv: KVView, scale: float, window: int = 0,
                    n_splits: int = 1, part_ml: Optional[torch.Tensor] = None,
-                   part_o: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
-    """`sinks`: None, or float32 [q_heads]: exp(sinks[h]) joins the softmax denominator of head h (once, with no value)."""
+                   part_o: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
+    """`sinks`: None, or float32 [q_heads]: exp(sinks[h]) joins the softmax denominator of head h (once, with no value).
+    `keep_first`: with a window, the sequence's first keys that stay visible at any distance."""
     require_cuda(q, out, cu_seqlens, start_pos, part_ml, part_o, sinks)
     n_tokens = q.shape[0]
     assert q.dtype == out.dtype == kv.k_pool.dtype
@@ -243,7 +255,8 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_seqlens: torch.Tensor,
                                      start_pos.data_ptr(), n_seqs, n_tokens, max_q_len, q_heads, kv.kv_heads,
                                      kv.head_dim, float(scale), int(window), n_splits, _ptr(part_ml), _ptr(part_o),
                                      kv.k_pool.data_ptr(), kv.v_pool.data_ptr(), kv.page_table.data_ptr(),
-                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _ptr(sinks), _stream()), "attention")
+                                     kv.entry_offset, kv.pages_per_seq, kv.page_size, _ptr(sinks), int(keep_first), _stream()),
+           "attention")
     if n_splits > 1:
         count_launches(1)
 
@@ -517,6 +530,135 @@ def gates_scan_step(u: torch.Tensor, w_r_t: torch.Tensor, w_i_t: torch.Tensor, b
                                       lam.data_ptr(), float(c), _columns(y, y_col), y.stride(0), _ptr(y_bias), state.data_ptr(),
                                       state.stride(0), step.slots.data_ptr(), n, W, B, float(out_scale), out.data_ptr(),
                                       dtype_code(out.dtype), _stream()), "recurrence gates and step")
+
+
+# ------------------------------------------------------------------ mixture of experts (csrc/mixture.cu)
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Per token the `top` largest of logits + bias (float32 [n, E]; the lower index wins a tie) into ids int32 [n, top],
+    and the softmax over those chosen logits into weights float32 [n, top]."""
+    require_cuda(logits, bias, ids, weights)
+    n, E = logits.shape
+    assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    assert ids.shape == (n, top) and weights.shape == (n, top) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == E))
+    _check(core().mlc_moe_route(logits.data_ptr(), _ptr(bias), n, E, int(top), ids.data_ptr(), weights.data_ptr(), _stream()),
+           "expert routing")
+
+
+def moe_plan_rows(n_pairs: int, n_experts: int, tile: int) -> int:
+    """Rows the sorted order of `n_pairs` (token, expert) pairs can take when every expert's run is rounded up to whole
+    tiles: only experts that were chosen have a run."""
+    most = n_pairs + min(n_experts, n_pairs) * (tile - 1)
+    return max(tile, most - most % tile)
+
+
+def moe_plan(ids: torch.Tensor, n_experts: int, tile: int, row_of: torch.Tensor, src_tok: torch.Tensor,
+             tile_expert: torch.Tensor) -> None:
+    """The order of a step's (token, choice) pairs by expert, made on the device: row_of int32 [n, top] (a pair's row),
+    src_tok int32 [rows] (a row's token, -1: padding), tile_expert int32 [rows / tile] (a tile's expert, -1: none)."""
+    require_cuda(ids, row_of, src_tok, tile_expert)
+    n, top = ids.shape
+    assert ids.dtype == row_of.dtype == src_tok.dtype == tile_expert.dtype == torch.int32 and row_of.shape == ids.shape
+    rows = src_tok.numel()
+    assert rows % tile == 0 and tile_expert.numel() == rows // tile
+    _check(core().mlc_moe_plan(ids.data_ptr(), n * top, top, int(n_experts), int(tile), rows, row_of.data_ptr(),
+                               src_tok.data_ptr(), tile_expert.data_ptr(), _stream()), "expert plan")
+
+
+def grouped_linear(x: torch.Tensor, src_tok: Optional[torch.Tensor], w: torch.Tensor, tile_expert: torch.Tensor, tile: int,
+                   out: torch.Tensor) -> None:
+    """out[row] = w[expert of the row's tile] · x[src_tok[row]] (x[row] without src_tok), float32 multiply-adds;
+    w [E, N, K], out [rows, N]; padding rows are not written."""
+    require_cuda(x, src_tok, w, tile_expert, out)
+    E, N, K = w.shape
+    rows = out.shape[0]
+    assert x.shape[1] == K and out.shape[1] == N and rows % tile == 0 and tile_expert.numel() == rows // tile
+    assert src_tok is None or src_tok.numel() == rows
+    _check(core().mlc_grouped_linear(x.data_ptr(), dtype_code(x.dtype), _ptr(src_tok), w.data_ptr(), dtype_code(w.dtype),
+                                     tile_expert.data_ptr(), int(tile), rows, N, K, out.data_ptr(), dtype_code(out.dtype),
+                                     _stream()), "grouped product")
+
+
+def moe_gather(x: torch.Tensor, src_tok: torch.Tensor, rows: torch.Tensor) -> None:
+    """rows[r] = x[src_tok[r]], zeros where src_tok[r] < 0."""
+    require_cuda(x, src_tok, rows)
+    assert x.dtype == rows.dtype and rows.shape == (src_tok.numel(), x.shape[1])
+    _check(core().mlc_moe_gather(x.data_ptr(), dtype_code(x.dtype), src_tok.data_ptr(), rows.shape[0], x.shape[1],
+                                 rows.data_ptr(), _stream()), "expert gather")
+
+
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_j weights[t, j] · y[row_of[t, j]], float32, j in order."""
+    require_cuda(y, row_of, weights, out)
+    n, top = row_of.shape
+    assert y.dtype == out.dtype == weights.dtype == torch.float32 and out.shape == (n, y.shape[1])
+    _check(core().mlc_moe_combine(y.data_ptr(), row_of.data_ptr(), weights.data_ptr(), n, top, y.shape[1], out.data_ptr(),
+                                  _stream()), "expert combine")
+
+
+def scaled_add(x: torch.Tensor, y1: torch.Tensor, s1: Optional[torch.Tensor], y2: Optional[torch.Tensor] = None,
+               s2: Optional[torch.Tensor] = None) -> None:
+    """x (float32 [n, d], in place) += s1 · y1 (+ s2 · y2): y float32 [n, d] or slices [s, n, d] that are added up first,
+    s float32 [d] per-channel factors (None: one)."""
+    require_cuda(x, y1, s1, y2, s2)
+    n, d = x.shape
+    for y in (y1, y2):
+        assert y is None or (y.dtype == torch.float32 and tuple(y.shape[-2:]) == (n, d))
+    for f in (s1, s2):
+        assert f is None or (f.dtype == torch.float32 and f.numel() == d)
+    sl = lambda y: (y.shape[0] if y is not None and y.dim() == 3 else 1)
+    _check(core().mlc_scaled_add(x.data_ptr(), y1.data_ptr(), sl(y1), _ptr(s1), _ptr(y2), sl(y2), _ptr(s2), n, d, _stream()),
+           "scaled addition")
+
+
+# ------------------------------------------------------------------ gated linear attention (csrc/linear_attention.cu)
+def gla(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, z_bias: Optional[torch.Tensor], tau: float,
+        state: torch.Tensor, step, heads: int, dim: int, vdim: int, out: torch.Tensor) -> None:
+    """S <- diag(sigmoid(z + bias)^(1/tau)) S + k vT, o = ST q dim^-1/2 over the step's tokens; q, k (heads x dim) and v
+    (heads x vdim) in the float32 rows `proj`, z float32 [n, heads*dim], state float32 [slots, heads*vdim*dim],
+    out float32 [n, heads*vdim]."""
+    require_cuda(z, z_bias, out)
+    _require_rows(state)
+    n = proj.shape[0]
+    assert z.dtype == out.dtype == torch.float32 and z.shape == (n, heads * dim) and out.shape == (n, heads * vdim)
+    assert state.shape[1] == heads * dim * vdim
+    _check(core().mlc_gla(_columns(proj, 0), proj.stride(0), q_col, k_col, v_col, z.data_ptr(), _ptr(z_bias), float(tau),
+                          state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs, n,
+                          heads, dim, vdim, out.data_ptr(), _stream()), "gated linear attention")
+
+
+# ------------------------------------------------------------------ latent attention (csrc/latent.cu)
+def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: int, gain: torch.Tensor, eps: float, positions: torch.Tensor,
+                   tok_seq: torch.Tensor, rope: Optional[torch.Tensor], heads: int, dim: int, rot: int, rank: int,
+                   q_out: torch.Tensor, kv: Optional[KVView]) -> None:
+    """From the float32 rows `proj` (query heads [dim | rot] at q_col, [rank | rot] at kv_col): the cache row
+    [normed latent | rotated shared key part | zeros] of every token (when `kv` is given), and the rotated query parts
+    into entries [rank, rank + rot) of q_out [n, heads, D] (zeros behind them)."""
+    require_cuda(proj, gain, positions, tok_seq, rope, q_out)
+    n = proj.shape[0]
+    D = q_out.numel() // max(1, n * heads)
+    assert proj.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == rank
+    assert rope is None or (rope.dtype == torch.float32 and rope.shape[1] * 2 == rot)
+    if kv is not None:
+        assert kv.k_pool.dtype == q_out.dtype and kv.head_dim == D and kv.kv_heads == 1
+        args = (1, kv.k_pool.data_ptr(), kv.page_table.data_ptr(), kv.entry_offset, kv.pages_per_seq, kv.page_size)
+    else:
+        args = (0, None, None, 0, 0, 1)
+    _check(core().mlc_latent_prepare(proj.data_ptr(), proj.stride(0), q_col, kv_col, gain.data_ptr(), float(eps),
+                                     positions.data_ptr(), tok_seq.data_ptr(), _ptr(rope), rope.shape[0] if rope is not None else 0,
+                                     n, heads, dim, rot, rank, D, q_out.data_ptr(), dtype_code(q_out.dtype), *args, _stream()),
+           "latent norm, rotation and cache write")
+
+
+def head_project(src: torch.Tensor, src_strides, w: torch.Tensor, w_strides, out: torch.Tensor, out_strides, n: int, heads: int,
+                 n_in: int, n_out: int, src_offset: int = 0, out_offset: int = 0) -> None:
+    """out[t, h, j] = sum_d src[t, h, d] · w[h, d, j] per head with float32 multiply-adds.  Strides in elements:
+    src (token, head), w (head, d, j), out (token, head); offsets in elements from each tensor's start."""
+    require_cuda(src, w, out)
+    lib = core()
+    _check(lib.mlc_head_project(src.data_ptr() + src_offset * src.element_size(), dtype_code(src.dtype), src_strides[0], src_strides[1],
+                                w.data_ptr(), dtype_code(w.dtype), w_strides[0], w_strides[1], w_strides[2],
+                                out.data_ptr() + out_offset * out.element_size(), dtype_code(out.dtype), out_strides[0], out_strides[1],
+                                n, heads, n_in, n_out, _stream()), "per-head product")
 
 
 class PinnedCopy:

@@ -161,8 +161,9 @@ class GQAttention(Part):
         """Attention of the step's tokens over the cache entry `kv` (which already holds their keys)."""
         rt = self.runtime
         window = self.window or 0
+        keep = getattr(self, "keep_first", 0) if window else 0     # first keys that stay visible beside the window
         sinks = getattr(self, "sinks", None)          # float32 [heads] or None: a logit per head that joins every softmax
-        if self.use_tensor_cores:
+        if self.use_tensor_cores and not keep:
             row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
                                                              self.KV, rt.n_sms)
             if (step.max_q_len >= 16 and n_splits == 1
@@ -188,7 +189,7 @@ class GQAttention(Part):
             part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
             part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
         kernels.attention_simt(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                               self.scale, window, n_splits, part_ml, part_o, sinks=sinks)
+                               self.scale, window, n_splits, part_ml, part_o, sinks=sinks, keep_first=keep)
 
 
 def choose_splits(step, q_heads: int, kv_heads: int, n_sms: int, tokens_per_block: int, keys_per_split: int = 256,
@@ -238,10 +239,11 @@ class SinkAttention(GQAttention):
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
                  scale: float, norm_eps: float, position: PartSpec, qk_norm: bool = True, sink: bool = True,
-                 window: Optional[int] = None, value_scale: float = 1.0, names: Optional[dict] = None):
+                 window: Optional[int] = None, value_scale: float = 1.0, names: Optional[dict] = None, keep_first: int = 0):
+        """`window`, `keep_first`: position i sees j <= i with i - j < window or j < keep_first (no window: every j <= i)."""
         Part.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                       v_head_dim=v_head_dim, scale=scale, norm_eps=norm_eps, qk_norm=qk_norm, sink=sink, window=window,
-                      value_scale=value_scale)
+                      value_scale=value_scale, keep_first=keep_first)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden, self.H, self.KV = int(hidden_size), int(num_heads), int(num_kv_heads)
@@ -254,6 +256,7 @@ class SinkAttention(GQAttention):
         self.scale, self.eps = float(scale), float(norm_eps)
         self.qk_norm, self.has_sink = bool(qk_norm), bool(sink)
         self.window = int(window) if window else None
+        self.keep_first = max(0, int(keep_first)) if self.window else 0
         self.value_scale = float(value_scale)
         self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
         self.position = build_part(position, name)
@@ -271,7 +274,7 @@ class SinkAttention(GQAttention):
         return specs
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed("window" if self.window else "all", self.KV, self.hd, self.window)
+        return CacheNeed("window" if self.window else "all", self.KV, self.hd, self.window, self.keep_first)
 
     def bind(self, get, runtime):
         Part.bind(self, get, runtime)
@@ -325,3 +328,93 @@ class SinkAttention(GQAttention):
             self.in_proj = fused_rows(self._in, self.runtime)
         o = self.mix(self.in_proj(h, torch.float32), 0, step, memory)
         return self.o(o, torch.float32, partial_ok=True)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(GQAttention):
+    """Attention whose keys and values are expansions of a low-rank latent (the "multi-head latent attention" of
+    DeepSeek-V2).  Per token, with H heads, `dim` unrotated and `rot_dim` rotated query/key entries per head, values of
+    `v_head_dim`, a latent of `kv_rank`:
+
+        q = W_q h, head by head [dim | rot_dim];      [c_raw | k_rot] = W_dkv h  (kv_rank + rot_dim rows)
+        c = c_raw / rms(c_raw) · g  (eps inside the root),   k_rot and the rot_dim part of every q head are rotated
+        k_h = [W_uk,h c | k_rot],  v_h = W_uv,h c,  score = scale · q_h · k_h,  causal softmax,  out = W_o [heads' sums]
+
+    Only [c | k_rot] is cached: one row of D = ceil16(kv_rank + rot_dim) entries per token, one "key/value head" that all
+    query heads read, the values being the row's first kv_rank entries (`CacheNeed.shared_kv`).  The two expansions
+    move to the query side: q'_h = [W_uk,hᵀ q_h,plain | q_h,rot] meets the cached rows directly, and W_uv,h is applied
+    to the head's weighted sum of latents, so a step never expands the keys and values of the tokens before it.  The
+    attention kernels are the ones every other attention uses.
+
+    `names`: the tensors' names below the part's prefix, by role (q, dkv, dkv_norm, uk, uv, o)."""
+    graph_safe = True
+    accumulates = False
+
+    NAMES = dict(q="q", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", o="o")
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, kv_rank: int,
+                 scale: float, norm_eps: float, position: PartSpec, names: Optional[dict] = None):
+        Part.__init__(self, name, hidden_size=hidden_size, num_heads=num_heads, head_dim=head_dim, rot_dim=rot_dim,
+                      v_head_dim=v_head_dim, kv_rank=kv_rank, scale=scale, norm_eps=norm_eps)
+        self.hidden, self.H, self.KV = int(hidden_size), int(num_heads), 1
+        self.dim, self.rot, self.vdim, self.rank = int(head_dim), int(rot_dim), int(v_head_dim), int(kv_rank)
+        if self.rot % 2 or self.rot < 0 or self.dim < 0 or self.dim + self.rot <= 0:
+            raise ValueError(f"latent attention: a head has {head_dim} plain and {rot_dim} rotated entries; the rotated size must be even")
+        self.hd = (self.rank + self.rot + 15) // 16 * 16              # a cached row, and a query row, in the kernels
+        if self.hd > 256:
+            raise ValueError(f"latent attention: kv_rank + rot_dim up to 256 is supported, got {self.rank + self.rot}")
+        if not scale > 0:
+            raise ValueError(f"latent attention: the score's scale must be positive, got {scale}")
+        self.scale, self.eps = float(scale), float(norm_eps)
+        self.window = None
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+        self.position = build_part(position, name)
+
+    def tensors(self):
+        t, H = self.t, self.H
+        return [TensorSpec(t["q"], (H * (self.dim + self.rot), self.hidden)),
+                TensorSpec(t["dkv"], (self.rank + self.rot, self.hidden)),
+                TensorSpec(t["dkv_norm"], (self.rank,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["uk"], (H * self.dim, self.rank)), TensorSpec(t["uv"], (H * self.vdim, self.rank)),
+                TensorSpec(t["o"], (self.hidden, H * self.vdim))]
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("all", 1, self.hd, None, 0, True)
+
+    def bind(self, get, runtime):
+        Part.bind(self, get, runtime)
+        t = self.t
+        self.in_proj = fused_rows([get(t["q"]), get(t["dkv"])], runtime)
+        self.kv_col = self.H * (self.dim + self.rot)
+        self.gain = get(t["dkv_norm"]).to(torch.float32).contiguous()
+        self.w_uk, self.w_uv = get(t["uk"]).contiguous(), get(t["uv"]).contiguous()
+        self.o = Linear(get(t["o"]), runtime)
+        self.use_tensor_cores = runtime.dtype == torch.bfloat16
+        if self.use_tensor_cores:
+            kernels.attention_library(self.hd)
+
+    def weight_bytes(self) -> int:
+        return (self.in_proj.nbytes() + self.o.nbytes()
+                + sum(w.numel() * w.element_size() for w in (self.w_uk, self.w_uv)))
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
+        rt = self.runtime
+        n, H, D = h.shape[0], self.H, self.hd
+        proj = self.in_proj(h, torch.float32)
+        table = self.position.table_for(step.max_kv_len) if self.rot and hasattr(self.position, "table_for") else None
+        q = rt.empty(n, H * D)
+        kernels.latent_prepare(proj, 0, self.kv_col, self.gain, self.eps, step.positions, step.tok_seq, table, H, self.dim,
+                               self.rot, self.rank, q, memory.kv if memory.writes_cache else None)
+        if self.dim:
+            # the key expansion on the query's side: q'[t, h, :rank] = W_uk,hᵀ q_plain[t, h]
+            kernels.head_project(proj, (proj.stride(0), self.dim + self.rot), self.w_uk, (self.dim * self.rank, self.rank, 1),
+                                 q, (H * D, D), n, H, self.dim, self.rank)
+        else:
+            q.view(n, H, D)[:, :, :self.rank].zero_()
+        o = rt.empty(n, H * D)
+        self.attend(q, o, step, memory.kv)
+        # the value expansion behind the sum: val[t, h] = W_uv,h (sum_j p c_j)
+        val = rt.empty(n, H * self.vdim)
+        kernels.head_project(o, (H * D, D), self.w_uv, (self.vdim * self.rank, 1, self.rank), val, (H * self.vdim, self.vdim),
+                             n, H, self.rank, self.vdim)
+        return self.o(val, torch.float32, partial_ok=True)

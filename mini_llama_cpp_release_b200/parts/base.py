@@ -43,19 +43,26 @@ class TensorSpec:
     optional: bool = False
     init: str = "normal"        # "normal": N(0, std); "one_plus_normal": 1 + N(0, std)
     stored: bool = True         # False: not a tensor of its own in the file (an alias of another part's)
+    # A size of -1 in `shape` is one that only the file gives (no key of the configuration names it): any size fits, and
+    # the part reads it off the tensor when it binds.  `default_shape` is what the random-weights mode writes then.
+    default_shape: Optional[Tuple[int, ...]] = None
 
 
 @dataclass(frozen=True)
 class CacheNeed:
     """Keys and values a mixer keeps per sequence.  kind "all": every position; "window":
-    only the last `window` positions are ever read."""
+    only the last `window` positions are ever read, and beside them the sequence's first
+    `keep_first` positions, which are never given back.  `shared_kv`: the values are read
+    out of the key rows (their first entries), so the entry has one pool, not two."""
     kind: str
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
+    shared_kv: bool = False
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.keep_first, self.shared_kv)
 
 
 @dataclass(frozen=True)

@@ -14,7 +14,7 @@ import torch
 from .. import kernels
 from ..config.registry import register_part, build_part
 from ..config.specs import PartSpec
-from .base import MixerMemory, Part
+from .base import MixerMemory, Part, TensorSpec
 
 
 @register_part("block", "prenorm")
@@ -101,3 +101,90 @@ class BranchNormBlock(Part):
             if h is not None:
                 step.handover[self.COPY] = (x, h)
         return x, None
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Part):
+    """One norm, two branches that both read it: h = norm(x); x <- x + s1 * mixer(h) + s2 * feed_forward(h).
+    s1 and s2 are per-channel factors ("layer scale") stored as tensors; without them the factors are one.  The
+    feed-forward may be absent.  The sum is float32: the branches return float32 (or partial sums), and one kernel
+    multiplies, adds them up and adds them into the stream."""
+    graph_safe = True
+
+    def __init__(self, name: str, mixer: PartSpec, norm: PartSpec, feed_forward: Optional[PartSpec] = None,
+                 layer_scale: bool = False, names: Optional[dict] = None):
+        super().__init__(name, layer_scale=layer_scale)
+        names = names or {}
+        self.norm = build_part(norm, name + names.get("norm", "norm."))
+        self.mixer = build_part(mixer, name + names.get("mixer", "mixer."))
+        self.feed_forward = build_part(feed_forward, name + names.get("feed_forward", "feed_forward.")) if feed_forward else None
+        self.layer_scale = bool(layer_scale)
+        self.t_s1 = name + names.get("mixer_scale", "mixer_scale")
+        self.t_s2 = name + names.get("feed_forward_scale", "feed_forward_scale")
+        self.s1 = self.s2 = None
+
+    def children(self):
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    def tensors(self):
+        if not self.layer_scale:
+            return []
+        size = self.norm.size
+        specs = [TensorSpec(self.t_s1, (size,), role="gain", init="one_plus_normal")]
+        if self.feed_forward is not None:
+            specs.append(TensorSpec(self.t_s2, (size,), role="gain", init="one_plus_normal"))
+        return specs
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        if self.layer_scale:
+            self.s1 = get(self.t_s1).to(torch.float32).contiguous()
+            self.s2 = get(self.t_s2).to(torch.float32).contiguous() if self.feed_forward is not None else None
+
+    def weight_bytes(self) -> int:
+        return super().weight_bytes() + sum(s.numel() * 4 for s in (self.s1, self.s2) if s is not None)
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], step, memory: MixerMemory
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        h = self.norm.forward(x, pending)
+        y = self.mixer.forward(h, step, memory)
+        f = self.feed_forward.forward(h, step) if self.feed_forward is not None else None
+        kernels.scaled_add(x, y, self.s1, f, self.s2)
+        return x, None
+
+
+@register_part("block", "stream_mix")
+class StreamMix(Part):
+    """Not a layer but a step between layers: x <- W [x ; e], with e the embedding's output of the step's tokens and W
+    [size, 2 size] (the stream's columns first).  A model that walks a run of its layers several times places one
+    before each walk.  It keeps nothing per sequence.  The model's step function leaves e in the step's `handover`
+    under `EMBEDDING` when a block asks for it (`reads_embedding`)."""
+    graph_safe = True
+    reads_embedding = True
+    EMBEDDING = "embedding_output"
+
+    def __init__(self, name: str, size: int, tensor: str = "weight"):
+        super().__init__(name, size=size, tensor=tensor)
+        self.size = int(size)
+        self.tensor = name + tensor
+
+    def tensors(self):
+        return [TensorSpec(self.tensor, (self.size, 2 * self.size))]
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        from .linear import Linear
+        self.w = Linear(get(self.tensor), runtime)
+
+    def weight_bytes(self) -> int:
+        return self.w.nbytes()
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], step, memory: MixerMemory
+                ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if pending is not None:
+            x.add_(pending.sum(dim=0) if pending.dim() == 3 else pending)
+        e = step.handover[self.EMBEDDING]
+        both = self.runtime.empty(x.shape[0], 2 * self.size)
+        both[:, :self.size].copy_(x)
+        both[:, self.size:].copy_(e)
+        return self.w(both, torch.float32), None

@@ -70,3 +70,89 @@ class SwiGLU(Part):
             self.down.add_into(a, residual)
             return None
         return self.down(a, torch.float32, partial_ok=True)
+
+
+@register_part("feed_forward", "mixture")
+class MixtureOfExperts(Part):
+    """A mixture of SwiGLU experts.  Router logits z = W_r h + b_r in float32; each token uses the `top` experts with the
+    largest logits, weighted by the softmax over those chosen logits only; the output is the weighted sum of the
+    chosen experts' outputs.  Experts have no biases.
+
+    On the device and without a word to the host: the step's (token, expert) pairs are sorted by expert into runs that
+    start on tile borders (`kernels.moe_plan`), every run's rows are multiplied by that expert's matrices, and each
+    token adds up its rows with its weights, in the order of its choices.
+
+    `names`: the tensors' names below the part's prefix, by role: router, router_bias, and the pattern of an expert's
+    prefix (`expert`, with {e} for its number) before gate / up / down."""
+    graph_safe = True
+
+    NAMES = dict(router="router", router_bias="router.b", expert="e{e}.", gate="gate", up="up", down="down")
+    TILE = 64                        # rows per block of the grouped product; an expert's run is padded to it
+
+    def __init__(self, name: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 router_bias: bool = True, names: Optional[dict] = None):
+        super().__init__(name, hidden_size=hidden_size, intermediate_size=intermediate_size, num_experts=num_experts, top=top,
+                         router_bias=router_bias)
+        self.hidden, self.inter, self.E, self.top = int(hidden_size), int(intermediate_size), int(num_experts), int(top)
+        if not 1 <= self.top <= self.E or self.top > 32 or self.E > 256:
+            raise ValueError(f"mixture of experts: top {top} of {num_experts} experts is not supported (top <= 32, experts <= 256)")
+        self.has_bias = bool(router_bias)
+        self.t = {**self.NAMES, **(names or {})}
+
+    def _expert(self, e: int, role: str) -> str:
+        return self.name + self.t["expert"].format(e=e) + self.t[role]
+
+    def tensors(self):
+        specs = [TensorSpec(self.name + self.t["router"], (self.E, self.hidden))]
+        if self.has_bias:
+            specs.append(TensorSpec(self.name + self.t["router_bias"], (self.E,), role="bias"))
+        for e in range(self.E):
+            specs += [TensorSpec(self._expert(e, "gate"), (self.inter, self.hidden)),
+                      TensorSpec(self._expert(e, "up"), (self.inter, self.hidden)),
+                      TensorSpec(self._expert(e, "down"), (self.hidden, self.inter))]
+        return specs
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        self.router = get(self.name + self.t["router"]).to(torch.float32).contiguous()        # the router is float32 in both modes
+        self.router_bias = get(self.name + self.t["router_bias"]).to(torch.float32).contiguous() if self.has_bias else None
+        # [E, 2*inter, hidden]: an expert's gate rows, then its up rows; [E, hidden, inter]
+        self.gate_up = torch.stack([torch.cat([get(self._expert(e, "gate")), get(self._expert(e, "up"))], dim=0)
+                                    for e in range(self.E)]).contiguous()
+        self.down = torch.stack([get(self._expert(e, "down")) for e in range(self.E)]).contiguous()
+
+    def weight_bytes(self) -> int:
+        """Bytes a step of many tokens reads; a step of few tokens reads `top` experts per token at most."""
+        return (self.gate_up.numel() * self.gate_up.element_size() + self.down.numel() * self.down.element_size()
+                + self.router.numel() * 4)
+
+    def route(self, h: torch.Tensor):
+        """(ids int32 [n, top], weights float32 [n, top])."""
+        rt = self.runtime
+        n = h.shape[0]
+        logits = rt.empty(n, self.E, dtype=torch.float32)
+        kernels.linear_simt(h, self.router, logits)
+        ids = rt.empty(n, self.top, dtype=torch.int32)
+        weights = rt.empty(n, self.top, dtype=torch.float32)
+        kernels.moe_route(logits, self.router_bias, self.top, ids, weights)
+        return ids, weights
+
+    def forward(self, h: torch.Tensor, step=None, residual=None):
+        rt = self.runtime
+        n = h.shape[0]
+        ids, weights = self.route(h)
+        tile = self.TILE
+        rows = kernels.moe_plan_rows(n * self.top, self.E, tile)
+        row_of = rt.empty(n, self.top, dtype=torch.int32)
+        src_tok = rt.empty(rows, dtype=torch.int32)
+        tile_expert = rt.empty(rows // tile, dtype=torch.int32)
+        kernels.moe_plan(ids, self.E, tile, row_of, src_tok, tile_expert)
+        gu = rt.empty(rows, 2 * self.inter)
+        kernels.grouped_linear(h, src_tok, self.gate_up, tile_expert, tile, gu)
+        act = rt.empty(rows, self.inter)
+        kernels.silu_mul(gu, act)
+        y = rt.empty(rows, self.hidden, dtype=torch.float32)
+        kernels.grouped_linear(act, None, self.down, tile_expert, tile, y)
+        out = rt.empty(n, self.hidden, dtype=torch.float32)
+        kernels.moe_combine(y, row_of, weights, out)
+        return out

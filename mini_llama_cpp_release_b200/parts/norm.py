@@ -20,17 +20,21 @@ from .base import Part, TensorSpec
 class RMSNorm(Part):
     graph_safe = True
 
-    def __init__(self, name: str, size: int, eps: float):
-        super().__init__(name, size=size, eps=eps)
+    def __init__(self, name: str, size: int, eps: float, tensor: str = "weight", offset: float = 0.0):
+        """`tensor`: the gain's name below the part's prefix.  `offset` is added to the stored values: a gain that is
+        stored around zero and applied as 1 + w has offset 1."""
+        super().__init__(name, size=size, eps=eps, tensor=tensor, offset=offset)
         self.size = int(size)
         self.eps = float(eps)
+        self.offset = float(offset)
+        self.tensor = self.name + tensor
 
     def tensors(self):
-        return [TensorSpec(self.name + "weight", (self.size,), role="gain", init="one_plus_normal")]
+        return [TensorSpec(self.tensor, (self.size,), role="gain", init="normal" if self.offset else "one_plus_normal")]
 
     def bind(self, get, runtime):
         super().bind(get, runtime)
-        self.gain = get(self.name + "weight").to(torch.float32).contiguous()
+        self.gain = (get(self.tensor).to(torch.float32) + self.offset).contiguous()
 
     def weight_bytes(self) -> int:
         return self.gain.numel() * 4

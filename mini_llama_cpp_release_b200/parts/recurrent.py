@@ -106,6 +106,86 @@ class GatedDeltaMixer(Part):
         return self.o(act, torch.float32, partial_ok=True)
 
 
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(Part):
+    """Gated linear attention (Yang, Wang, Shen, Panda, Kim, "Gated Linear Attention Transformers with Hardware-Efficient
+    Training"): per head a matrix memory S [dim, vdim] whose rows decay at rates of their own.
+
+        q = W_q h · dim^-1/2,  k = W_k h  (heads x dim);   v = W_v h  (heads x vdim)
+        a = sigmoid(W_a2 (W_a1 h) + b_a2)^(1/tau)          (heads x dim, a low-rank product; the rank is the tensors' own)
+        S_t = diag(a_t) S_{t-1} + k_t v_tᵀ;   o_t = S_tᵀ q_t
+        out = W_o ( o / rms(o) · w_norm · silu(W_g h) )     (rms over vdim per head, w_norm shared by the heads)
+
+    State per sequence: S for every head, float32, zero at the start.  Decays, their logarithms and the whole
+    recurrence are float32 in both engine modes.  `names`: the tensors' names below the part's prefix, by role."""
+    graph_safe = True
+
+    NAMES = dict(q="q", k="k", v="v", g="g", o="o", norm="norm", a1="a1", a2="a2", a2_bias="a2.b")
+    DEFAULT_DECAY_RANK = 16          # what the random-weights mode writes when no tensor says
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int, tau: float, norm_eps: float,
+                 decay_rank: Optional[int] = None, names: Optional[dict] = None):
+        super().__init__(name, hidden_size=hidden_size, num_heads=num_heads, head_dim=head_dim, v_head_dim=v_head_dim, tau=tau,
+                         norm_eps=norm_eps, decay_rank=decay_rank)
+        if not 1 <= head_dim <= 256:
+            raise ValueError(f"gated linear attention: key sizes up to 256 are supported, got {head_dim}")
+        if not tau > 0:
+            raise ValueError(f"gated linear attention: tau must be positive, got {tau}")
+        self.hidden, self.H, self.dim, self.vdim = int(hidden_size), int(num_heads), int(head_dim), int(v_head_dim)
+        self.tau, self.eps = float(tau), float(norm_eps)
+        self.decay_rank = int(decay_rank) if decay_rank else None
+        self.t = {role: name + n for role, n in {**self.NAMES, **(names or {})}.items()}
+        self.n_qk, self.n_v = self.H * self.dim, self.H * self.vdim
+
+    def tensors(self):
+        t, hid = self.t, self.hidden
+        r = self.decay_rank if self.decay_rank else -1
+        dr = self.decay_rank or self.DEFAULT_DECAY_RANK
+        return [TensorSpec(t["q"], (self.n_qk, hid)), TensorSpec(t["k"], (self.n_qk, hid)), TensorSpec(t["v"], (self.n_v, hid)),
+                TensorSpec(t["g"], (self.n_v, hid)), TensorSpec(t["o"], (hid, self.n_v)),
+                TensorSpec(t["norm"], (self.vdim,), role="gain", init="one_plus_normal"),
+                TensorSpec(t["a1"], (r, hid), default_shape=(dr, hid)),
+                TensorSpec(t["a2"], (self.n_qk, r), default_shape=(self.n_qk, dr)),
+                TensorSpec(t["a2_bias"], (self.n_qk,), role="bias")]
+
+    def cache_need(self):
+        return None
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.H * self.vdim * self.dim,), torch.float32)
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        t = self.t
+        a1, a2 = get(t["a1"]), get(t["a2"])
+        if a1.shape[0] != a2.shape[1]:
+            raise ValueError(f"gated linear attention: {t['a1']} has {a1.shape[0]} rows but {t['a2']} has {a2.shape[1]} columns")
+        self.rank = int(a1.shape[0])
+        # columns of the input product: q | k | v | g | a1
+        self.in_proj = fused_rows([get(t[r]) for r in ("q", "k", "v", "g")] + [a1], runtime)
+        self.k_col, self.v_col = self.n_qk, 2 * self.n_qk
+        self.g_col = self.v_col + self.n_v
+        self.a_col = self.g_col + self.n_v
+        self.a2 = a2.contiguous()
+        self.a2_bias, self.gain = _f32(get(t["a2_bias"])), _f32(get(t["norm"]))
+        self.o = Linear(get(t["o"]), runtime)
+
+    def weight_bytes(self) -> int:
+        return self.in_proj.nbytes() + self.o.nbytes() + self.a2.numel() * self.a2.element_size()
+
+    def forward(self, h: torch.Tensor, step, memory: MixerMemory) -> torch.Tensor:
+        rt = self.runtime
+        n = h.shape[0]
+        proj = self.in_proj(h, torch.float32)
+        z = rt.empty(n, self.n_qk, dtype=torch.float32)
+        kernels.linear_simt(proj[:, self.a_col:self.a_col + self.rank].contiguous(), self.a2, z)
+        o = rt.empty(n, self.n_v, dtype=torch.float32)
+        kernels.gla(proj, 0, self.k_col, self.v_col, z, self.a2_bias, self.tau, memory.state, step, self.H, self.dim, self.vdim, o)
+        act = rt.empty(n, self.n_v)
+        kernels.gated_rmsnorm(o, proj, self.g_col, self.gain, self.eps, self.H, self.vdim, act)
+        return self.o(act, torch.float32, partial_ok=True)
+
+
 @register_part("mixer", "gated_linear_recurrence")
 class GatedLinearRecurrence(Part):
     """The recurrent block of Griffin (De et al., "Griffin: Mixing Gated Linear Recurrences with Local Attention for

@@ -112,6 +112,12 @@ def stretched_frequencies(dims: int, base: float, scaling: Optional[dict]) -> Tu
     f = np.power(float(base), -2.0 * i / dims)
     if not scaling:
         return f.astype(np.float32), 1.0
+    if "original" not in scaling:
+        # linear stretching: positions are divided by the factor, that is, every frequency is
+        factor = float(scaling["factor"])
+        if factor <= 0:
+            raise ValueError("rope scaling: factor must be positive")
+        return (f / factor).astype(np.float32), 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
     if factor <= 0 or original <= 0 or float(scaling["fast"]) <= 0 or float(scaling["slow"]) <= 0:
         raise ValueError("rope scaling: factor, original, fast and slow must be positive")

@@ -40,11 +40,16 @@ def expected_tensors(parts: Sequence[Part]) -> Dict[str, TensorSpec]:
             if old is None:
                 out[spec.name] = spec
                 continue
-            if tuple(old.shape) != tuple(spec.shape):
+            if tuple(old.shape) != tuple(spec.shape):        # (a size only the file gives, -1, must be asked for alike)
                 raise WeightError(f"two parts want tensor {spec.name} with different shapes: {old.shape} and {spec.shape}")
             if old.stored is False and spec.stored:
                 out[spec.name] = spec
     return out
+
+
+def shape_fits(found: Sequence[int], wanted: Sequence[int]) -> bool:
+    """Whether a stored shape is the wanted one; a wanted size of -1 is one that only the file gives."""
+    return len(found) == len(wanted) and all(w == -1 or int(f) == int(w) for f, w in zip(found, wanted))
 
 
 def compare(entries: Mapping[str, TensorEntry], specs: Mapping[str, TensorSpec],
@@ -54,7 +59,7 @@ def compare(entries: Mapping[str, TensorEntry], specs: Mapping[str, TensorSpec],
     unexpected = [n for n in entries
                   if n not in specs and n not in ignore_extra and not n.endswith(IGNORED_SUFFIXES)]
     wrong_shape = [f"{n}: file has {list(entries[n].shape)}, model wants {list(s.shape)}"
-                   for n, s in specs.items() if n in entries and tuple(entries[n].shape) != tuple(s.shape)]
+                   for n, s in specs.items() if n in entries and not shape_fits(entries[n].shape, s.shape)]
     wrong_type = []
     for n, s in specs.items():
         if n not in entries:

@@ -31,7 +31,8 @@ def tensor_seed(seed: int, name: str) -> int:
 def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, std: float = STD) -> torch.Tensor:
     g = torch.Generator(device="cpu")
     g.manual_seed(tensor_seed(seed, spec.name))
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32) * std
+    shape = spec.default_shape if (spec.default_shape is not None and -1 in tuple(spec.shape)) else spec.shape
+    t = torch.randn(tuple(shape), generator=g, dtype=torch.float32) * std
     if spec.init == "one_plus_normal":
         t = t + 1.0
     return t.to(dtype)
@@ -51,7 +52,8 @@ def write_random_model(config: ModelConfig, folder: str, seed: int, dtype: torch
     spec = build_model_spec(cfg)
     parts = build_parts(spec).all_parts()
     wanted = [s for s in expected_tensors(parts).values() if s.stored and not s.optional]
-    layout = [(s.name, dtype, tuple(s.shape)) for s in wanted]
+    layout = [(s.name, dtype, tuple(s.default_shape if (s.default_shape is not None and -1 in tuple(s.shape)) else s.shape))
+              for s in wanted]
     by_name: Dict[str, TensorSpec] = {s.name: s for s in wanted}
     save_safetensors_streamed(os.path.join(folder, "model.safetensors"), layout,
                               lambda name: random_tensor(by_name[name], seed, dtype, std),
