@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--config NAME] [--dtype bfloat16|float32]
     python bench.py --impl reference      # the reference project's own GPU path on the same work
-    python bench.py --compare mepolix-w896 [--layers 6]   # the Mepolix design beside Qwen2 at equal sizes (a line of its own)
+    python bench.py --compare mepolix-w896 [--layers 6]   # the Mepolix (or, kebesun-w896, the Kebesun) design beside Qwen2 at equal sizes (a line of its own)
 
 A "step" is one decode step of the whole batch.  The default run (`--config qwen2-0.5b`) has the layer sizes of a
 Qwen2-0.5B (24 layers, width 896, 14 query heads on 2 kv heads of size 64, feed-forward 4864, vocabulary 151936,
@@ -44,7 +44,8 @@ CONFIGS = {
     "qwen2-7b": dict(preset="qwen2-7b", prompt_len=2048, ctx_len=8192, ragged=None, max_steps=1000),
 }
 # a Mepolix preset → the Qwen2 preset it is timed beside (equal width, attention shape, feed-forward and vocabulary)
-COMPARE = {"mepolix-w896": "qwen2-0.5b", "mepolix-w1536": "qwen2-1.5b", "mepolix-w3584": "qwen2-7b"}
+COMPARE = {"mepolix-w896": "qwen2-0.5b", "mepolix-w1536": "qwen2-1.5b", "mepolix-w3584": "qwen2-7b",
+           "kebesun-w896": "qwen2-0.5b", "kebesun-w1536": "qwen2-1.5b", "kebesun-w3584": "qwen2-7b"}
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 REF_SOURCE = os.environ.get("MLC_REFERENCE_SOURCE", "/root/reference")     # where the reference's checkout lies, if baseline/_ref is empty
 REF_PREFILL_TOKENS = 32
@@ -145,10 +146,11 @@ def compare(args) -> int:
     steps, warmup = max(1, min(args.steps, 512)), max(3, args.warmup)
     out = {"compare": args.compare, "layers": layers, "batch": batch, "prompt_len": prompt_len, "dtype": args.dtype,
            "peaks": pk["source"]}
-    for label, preset in (("mepolix", args.compare), ("qwen2", COMPARE[args.compare])):
+    for label, preset in ((args.compare.split("-")[0], args.compare), ("qwen2", COMPARE[args.compare])):
         raw = dict(measure.PRESETS[preset])
         if "layers" in raw:
-            raw["layers"] = raw["layers"][-layers:]            # ends on a layer with attention beside the recurrence
+            # Mepolix: the last layers (they end on attention beside the recurrence); Kebesun: the first, one whole cycle
+            raw["layers"] = raw["layers"][-layers:] if raw.get("architecture") == "Mepolix" else raw["layers"][:layers]
         else:
             raw["num_hidden_layers"] = layers
         folder = measure.random_model_folder(raw, tag=f"compare_{preset}_L{layers}")
@@ -189,7 +191,7 @@ def main() -> int:
                     help="run one part only and print a short line (for profiling a small case)")
     ap.add_argument("--prompt-len", type=int, default=None, help="prompt length of the --only runs")
     ap.add_argument("--compare", default=None, choices=sorted(COMPARE),
-                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix preset beside the Qwen2 "
+                    help="instead of the benchmark line: prompt and decode throughput of a Mepolix or Kebesun preset beside the Qwen2 "
                          "preset of the same width, head shape and feed-forward, at --layers layers each (default 6)")
     args = ap.parse_args()
     if args.compare:

@@ -50,6 +50,7 @@ struct MmaArgs {
     int q_heads;
     int group;
     int window;
+    int keep_first;           // with a window: the sequence's first keys that stay visible at any distance
     int tokens_per_block;
     int heads_per_block;
     int head_chunks;
@@ -150,29 +151,37 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;
-    const int per_split = (tile_end - tile_begin + a.n_splits - 1) / a.n_splits;
-    const int my_begin = tile_begin + split * per_split;
-    const int my_end = min(tile_end, my_begin + per_split);
+    // Tiles of kept first keys that lie before the window's first tile are walked ahead of it: the walk's tile number v
+    // stands for tile v below `head_tiles` and for tile_begin + (v - head_tiles) from there on (`tile_of`).  my_begin
+    // and my_end count in walk numbers.
+    const int keep = (a.window > 0) ? a.keep_first : 0;
+    const int head_tiles = min(tile_begin, (keep + TILE - 1) / TILE);
+    const int walk = head_tiles + tile_end - tile_begin;
+    auto tile_of = [&](int v) { return v < head_tiles ? v : tile_begin + (v - head_tiles); };
+    const int per_split = (walk + a.n_splits - 1) / a.n_splits;
+    const int my_begin = split * per_split;
+    const int my_end = min(walk, my_begin + per_split);
 
     // the pages of this block's tiles, fetched once: a lookup in global memory per tile would put
     // its latency in front of every tile's copies
     __shared__ int tile_pages[MAX_TILES_STAGED];
     for (int t = my_begin + tid; t < my_end && t - my_begin < MAX_TILES_STAGED; t += 128)
-        tile_pages[t - my_begin] = __ldg(c.page_table + (long long)b * c.pages_per_seq + t);
+        tile_pages[t - my_begin] = __ldg(c.page_table + (long long)b * c.pages_per_seq + tile_of(t));
     __syncthreads();
 
     const bf16* kp = (const bf16*)c.k_pool;
     const bf16* vp = (const bf16*)c.v_pool;
-    auto load_tile = [&](int stage, int tile) {
-        const int page = (tile - my_begin < MAX_TILES_STAGED) ? tile_pages[tile - my_begin]
-                                                              : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
+    auto load_tile = [&](int stage, int v) {
+        const int tile = tile_of(v);
+        const int page = (v - my_begin < MAX_TILES_STAGED) ? tile_pages[v - my_begin]
+                                                           : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
         const long long base = c.entry_offset + ((long long)max(page, 0) * c.kv_heads + kvh) * TILE * HD;
         bf16* kd = Ks + stage * TILE * STRIDE;
         bf16* vd = Vs + stage * TILE * STRIDE;
         for (int idx = tid; idx < TILE * CPR; idx += 128) {
             const int j = idx / CPR, ch = idx % CPR;
             const int kpos = tile * TILE + j;
-            const bool valid = page >= 0 && kpos >= lo_block && kpos <= p_last;
+            const bool valid = page >= 0 && (kpos >= lo_block || kpos < keep) && kpos <= p_last;
             const long long off = valid ? base + (long long)j * HD + ch * 8 : 0;
             cp_async_16(kd + j * STRIDE + ch * 8, kp + off, valid);
             cp_async_16(vd + j * STRIDE + ch * 8, vp + off, valid);
@@ -219,15 +228,16 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
             ldmatrix_x4(qf[Q_IN_REGS ? kk : 0], Qs + (rt * 16 + (lane & 15)) * STRIDE + kk * 16 + (lane >> 4) * 8);
     }
 
-    for (int tile = my_begin, it = 0; tile < my_end; ++tile, ++it) {
+    for (int v = my_begin, it = 0; v < my_end; ++v, ++it) {
+        const int tile = tile_of(v);
         const int stage = it % NSTAGE;
-        if (tile + NSTAGE - 1 < my_end) load_tile((it + NSTAGE - 1) % NSTAGE, tile + NSTAGE - 1);
+        if (v + NSTAGE - 1 < my_end) load_tile((it + NSTAGE - 1) % NSTAGE, v + NSTAGE - 1);
         cp_async_commit();
         cp_async_wait<NSTAGE - 1>();
         __syncthreads();
 
         const int key0 = tile * TILE + part * KEYS_W;          // first key of this warp's part
-        if (warp_has_rows && key0 <= warp_hi && key0 + KEYS_W - 1 >= warp_lo) {
+        if (warp_has_rows && key0 <= warp_hi && (key0 + KEYS_W - 1 >= warp_lo || key0 < keep)) {
             const bf16* kt = Ks + stage * TILE * STRIDE + part * KEYS_W * STRIDE;
             const bf16* vt = Vs + stage * TILE * STRIDE + part * KEYS_W * STRIDE;
             float s[NT_S][4];
@@ -253,7 +263,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
             // mask (only where the tile meets the diagonal, a window's edge or the sequence's end), running maximum.
             // Scores stay unscaled; the scale rides in the exponent's multiply-add.
             float mx[2] = {-INFINITY, -INFINITY};
-            const bool interior = key0 + KEYS_W - 1 <= warp_first_pos && key0 >= warp_lo_last;   // the same for the whole warp
+            const bool interior = key0 + KEYS_W - 1 <= warp_first_pos && (key0 >= warp_lo_last || key0 + KEYS_W <= keep);   // the same for the whole warp
             if (interior) {
 #pragma unroll
                 for (int j = 0; j < NT_S; ++j) {
@@ -267,7 +277,7 @@ attention_mma_kernel(MmaArgs a, PagedKV c) {
                     for (int e = 0; e < 4; ++e) {
                         const int kpos = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
                         const int rr = e >> 1;
-                        const bool in_range = kpos >= row_lo[rr] && kpos <= row_hi[rr];
+                        const bool in_range = (kpos >= row_lo[rr] || kpos < keep) && kpos <= row_hi[rr];
                         const float v = in_range ? s[j][e] : -INFINITY;
                         s[j][e] = v;
                         mx[rr] = fmaxf(mx[rr], v);
@@ -506,9 +516,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / TILE, tile_end = p_last / TILE + 1;          // in 64-key pages
-    const int per_split = (tile_end - tile_begin + a.n_splits - 1) / a.n_splits;
-    const int my_begin = tile_begin + split * per_split;
-    const int my_end = min(tile_end, my_begin + per_split);
+    // pages of kept first keys before the window's first page are walked ahead of it; my_begin, my_end and the sub-tile
+    // numbers below count along that walk, `real_st` gives a walk number's true sub-tile
+    const int keep = (a.window > 0) ? a.keep_first : 0;
+    const int head_tiles = min(tile_begin, (keep + TILE - 1) / TILE);
+    const int walk = head_tiles + tile_end - tile_begin;
+    const int per_split = (walk + a.n_splits - 1) / a.n_splits;
+    const int my_begin = split * per_split;
+    const int my_end = min(walk, my_begin + per_split);
     __syncthreads();                           // the page list is in shared memory
     if (stamps) stamps[2] = stamp_ns();                                   // page list and position have arrived
 
@@ -522,7 +537,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     auto page_of = [&](int tile) {
         return (tile < D_TILES_STAGED) ? tile_pages[tile] : __ldg(c.page_table + (long long)b * c.pages_per_seq + tile);
     };
-    auto load_sub = [&](int stage, int st) {
+    auto real_st = [&](int vs) {
+        const int v = vs / SUB;
+        return (v < head_tiles ? v : tile_begin + (v - head_tiles)) * SUB + vs % SUB;
+    };
+    auto load_sub = [&](int stage, int vs) {
+        const int st = real_st(vs);
         const int tile = st / SUB;
         const int page = page_of(tile);
         if (D_TMA) {
@@ -549,7 +569,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         for (int idx = lane; idx < DKT * CPR; idx += 32) {
             const int j = idx / CPR, ch = idx % CPR;
             const int kpos = st * DKT + j;
-            const bool valid = page >= 0 && kpos >= lo_block && kpos <= p_last;
+            const bool valid = page >= 0 && (kpos >= lo_block || kpos < keep) && kpos <= p_last;
             const long long off = valid ? base + (long long)j * HD + ch * 8 : 0;
             cp_async_16(kd + j * STRIDE + ch * 8, kp + off, valid);
             cp_async_16(vd + j * STRIDE + ch * 8, vp + off, valid);
@@ -564,7 +584,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
     for (int p = 0; p < D_NSTAGE; ++p) {
         const int sp = st + DNW * p;
-        if (early == p && (sp >= st_end || sp * DKT + DKT - 1 < start)) {
+        if (early == p && (sp >= st_end || real_st(sp) * DKT + DKT - 1 < start)) {
             if (sp < st_end) load_sub(p, sp);
             if (!D_TMA) cp_async_commit();
             early = p + 1;
@@ -636,18 +656,18 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (st + DNW * (D_NSTAGE - 1) < st_end) load_sub((it + D_NSTAGE - 1) % D_NSTAGE, st + DNW * (D_NSTAGE - 1));
             if (!D_TMA) cp_async_commit();
         }
-        const int key0 = st * DKT;
+        const int key0 = real_st(st) * DKT;
         const unsigned kt_s = my_stages_s + (unsigned)(stage * D_STAGE_BYTES), vt_s = kt_s + D_OPER_BYTES;     // TMA form
         if (D_TMA) {
             if (!mbar_wait(my_bars + 8u * (unsigned)stage, (unsigned)(it / D_NSTAGE) & 1u, a.status, 31)) break;
             // keys outside the row tile's range, or of a page the sequence does not hold, count as zeros (their scores
             // are masked below, but a value row that is not a number would spoil 0 · v)
-            const int page = page_of(st / SUB);
-            if (page < 0 || key0 < lo_block || key0 + DKT - 1 > p_last) {
+            const int page = page_of(key0 / TILE);
+            if (page < 0 || (key0 < lo_block && key0 + DKT > keep) || key0 + DKT - 1 > p_last) {
                 for (int idx = lane; idx < DKT * CPR; idx += 32) {
                     const int j = idx / CPR, ch = idx % CPR;
                     const int kpos = key0 + j;
-                    if (page < 0 || kpos < lo_block || kpos > p_last) {
+                    if (page < 0 || (kpos < lo_block && kpos >= keep) || kpos > p_last) {
                         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d_swizzled(kt_s, j, ch)), "r"(z.x), "r"(z.y), "r"(z.z), "r"(z.w) : "memory");
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d_swizzled(vt_s, j, ch)), "r"(z.x), "r"(z.y), "r"(z.z), "r"(z.w) : "memory");
@@ -660,7 +680,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         __syncwarp();
 
-        if (key0 <= p_last && key0 + DKT - 1 >= lo_block) {
+        if (key0 <= p_last && (key0 + DKT - 1 >= lo_block || key0 < keep)) {
             const bf16* kt = my_stages + stage * 2 * D_STAGE;
             const bf16* vt = kt + D_STAGE;
             float sc[D_NT_S][4];
@@ -685,7 +705,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
             }
             float mx[2] = {-INFINITY, -INFINITY};
-            const bool all_visible = key0 >= all_lo && key0 + DKT - 1 <= all_hi;       // the same for the whole warp
+            const bool all_visible = (key0 >= all_lo || key0 + DKT <= keep) && key0 + DKT - 1 <= all_hi;       // the same for the whole warp
             if (all_visible) {
 #pragma unroll
                 for (int j = 0; j < D_NT_S; ++j) {
@@ -703,7 +723,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     for (int e = 0; e < 4; ++e) {
                         const int kpos = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
                         const int rr = e >> 1;
-                        const bool in_range = kpos >= row_lo[rr] && kpos <= row_hi[rr];
+                        const bool in_range = (kpos >= row_lo[rr] || kpos < keep) && kpos <= row_hi[rr];
                         const float v = in_range ? sc[j][e] * a.scale_log2 : -INFINITY;
                         sc[j][e] = v;
                         mx[rr] = fmaxf(mx[rr], v);
@@ -1011,7 +1031,8 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
                                  int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale,
                                  int window, int row_tiles, int warp_private, int n_splits, float* part_ml, float* part_o,
                                  void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
-                                 int pages_per_seq, int page_size, int pool_pages, int* status, const float* sinks, void* stream) {
+                                 int pages_per_seq, int page_size, int pool_pages, int* status, const float* sinks,
+                                 int keep_first, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (hd != HD || page_size != TILE) return MLC_ERR_BAD_SIZE;
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
@@ -1034,6 +1055,7 @@ extern "C" int mlc_attention_mma(const void* q, void* out, const int* cu_seqlens
     a.q_heads = q_heads;
     a.group = q_heads / kv_heads;
     a.window = window;
+    a.keep_first = keep_first < 0 ? 0 : keep_first;
     const int rows = 16 * row_tiles;
     a.heads_per_block = a.group < rows ? a.group : rows;
     a.tokens_per_block = rows / a.heads_per_block;

@@ -55,6 +55,7 @@ struct TcAttnArgs {
     int q_heads, kv_heads, group;
     int heads_per_block, tokens_per_block, head_chunks;
     int window;
+    int keep_first;           // with a window: the sequence's first keys that stay visible at any distance
     float scale_log2;
     const float* sinks;         // [q_heads] or null: exp(sinks[h]) joins head h's softmax denominator once, with no value
     int* status;
@@ -163,7 +164,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int p_first = start + tok0, p_last = start + tok0 + n_tok - 1;
     const int lo_block = (a.window > 0) ? max(0, p_first - a.window + 1) : 0;
     const int tile_begin = lo_block / A_BN;
-    const int n_tiles = (n_tok > 0) ? p_last / A_BN + 1 - tile_begin : 0;
+    // tiles of kept first keys before the window's first tile are walked ahead of it: walk number j stands for tile j
+    // below `head_tiles` and for tile_begin + (j - head_tiles) from there on
+    const int keep = (a.window > 0) ? a.keep_first : 0;
+    const int head_tiles = min(tile_begin, (keep + A_BN - 1) / A_BN);
+    auto tile_of = [&](int j) { return j < head_tiles ? j : tile_begin + (j - head_tiles); };
+    const int n_tiles = (n_tok > 0) ? head_tiles + p_last / A_BN + 1 - tile_begin : 0;
     const int* pages = a.page_table + (long long)b * a.pages_per_seq;
     const int seq_last = start + q_len - 1;                          // the sequence's last key
 
@@ -180,7 +186,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // complete, V_j the product that read its stage.  The thread looks at both in turn and never waits on one
             // while the other could go (K runs ahead of V by the score buffers and its ring).
             int jk = 0, jv = 0;
-            int page_k = __ldg(pages + tile_begin), page_v = page_k;
+            int page_k = __ldg(pages + tile_of(0)), page_v = page_k;
             unsigned long long deadline = 0;
             for (unsigned spin = 0; jk < n_tiles || jv < n_tiles; ++spin) {
                 bool moved = false;
@@ -190,7 +196,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     mbar_expect_tx(k_full(s), A_TILE_BYTES);
                     for (int kb = 0; kb < A_KB; ++kb)
                         tma_load_2d(k_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_k, kb * 64, row, k_full(s));
-                    if (++jk < n_tiles) page_k = __ldg(pages + tile_begin + jk);
+                    if (++jk < n_tiles) page_k = __ldg(pages + tile_of(jk));
                     moved = true;
                 }
                 if (jv < n_tiles && jv < jk && mbar_test(v_empty(jv % A_V_STAGES), ((jv / A_V_STAGES) & 1) ^ 1u)) {
@@ -199,7 +205,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     mbar_expect_tx(v_full(s), A_TILE_BYTES);
                     for (int kb = 0; kb < A_KB; ++kb)
                         tma_load_2d(v_base + s * A_TILE_BYTES + kb * A_BN * 128, &map_v, kb * 64, row, v_full(s));
-                    if (++jv < n_tiles) page_v = __ldg(pages + tile_begin + jv);
+                    if (++jv < n_tiles) page_v = __ldg(pages + tile_of(jv));
                     moved = true;
                 }
                 if (moved) {
@@ -252,7 +258,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!ok) break;
                 // the rows zero what lies beyond the sequence's end in the last V tile: told here that it has landed, since
                 // this thread alone follows the V stages' barriers phase by phase
-                if (j == n_tiles - 1 && (tile_begin + j) * A_BN + A_BN - 1 > seq_last) mbar_arrive(v_last);
+                if (j == n_tiles - 1 && tile_of(j) * A_BN + A_BN - 1 > seq_last) mbar_arrive(v_last);
                 ok = mbar_wait_polling(p_full(i), (unsigned)(j / A_AHEAD) & 1u, a.status, 12);
                 if (!ok) break;
                 tcgen05_fence_after();
@@ -303,9 +309,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             MLC_PHASE(0)                                   // waiting for the scores
             tcgen05_fence_after();
             const unsigned s_taddr = tmem_base + lane_base + (unsigned)(sbuf * A_BN);
-            const int key0 = (tile_begin + j) * A_BN;
+            const int key0 = tile_of(j) * A_BN;
             // decided for the warp as a whole: lanes that went separate ways here would run everything below twice
-            const bool masked = !__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && key0 >= lo);
+            const bool masked = !__all_sync(0xffffffffu, key0 + A_BN - 1 <= hi && (key0 >= lo || key0 + A_BN <= keep));
 
             // the row's 64 scores, read once and kept in registers
             float sc[A_BN];
@@ -315,7 +321,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int c = 0; c < A_BN; ++c) {
                     const int kpos = key0 + c;
-                    sc[c] = (kpos >= lo && kpos <= hi) ? sc[c] : -INFINITY;
+                    sc[c] = ((kpos >= lo || kpos < keep) && kpos <= hi) ? sc[c] : -INFINITY;
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one of 64 links
@@ -478,7 +484,7 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
                                      int n_tokens, int max_q_len, int q_heads, int kv_heads, int hd, float scale, int window,
                                      int* status, void* k_pool, void* v_pool, const int* page_table, long long entry_offset,
                                      int pages_per_seq, int page_size, long long pool_pages, long long* timing, const float* sinks,
-                                     void* stream) {
+                                     int keep_first, void* stream) {
 #if MLC_ATTENTION_TCGEN05
     if (hd != A_HD || page_size != A_BN) return MLC_ERR_UNSUPPORTED;
     if (n_seqs <= 0 || n_tokens <= 0 || max_q_len <= 0) return 0;
@@ -499,6 +505,7 @@ extern "C" int mlc_attention_tcgen05(const void* q, void* out, const int* cu_seq
     a.tokens_per_block = A_BM / a.heads_per_block;
     a.head_chunks = (group + a.heads_per_block - 1) / a.heads_per_block;
     a.window = window;
+    a.keep_first = keep_first < 0 ? 0 : keep_first;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.status = status;
     a.sinks = sinks;

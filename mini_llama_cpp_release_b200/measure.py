@@ -40,6 +40,25 @@ def _mepolix(width: int, ff: int, heads: int, kv_heads: int, head: int, n_layers
             "layers": [dict(par) if i % every == every - 1 else dict(delta) for i in range(n_layers)]}
 
 
+def _kebesun(width: int, ff: int, heads: int, kv_heads: int, head: int, n_layers: int, vocab: int) -> Dict[str, Any]:
+    """Kebesun layers of real width in a cycle of six: windowed attention, gated linear attention, latent attention,
+    windowed attention twice, gated linear attention.  The attention's shape (heads, kv heads, head size) and the width
+    are the Qwen2 preset's of the same width; the first layer of a cycle has that preset's dense feed-forward, the others
+    eight experts of half that size of which a token uses two, so every layer multiplies a token by as many weights as
+    the Qwen2 layer does.  No run of layers is repeated."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+           "rot": {"dims": head, "base": 1000000.0, "scaling": {"factor": 4.0}}, "mask": {"size": 1024, "keep_first": 4}}
+    lin = {"heads": max(1, heads // 2), "dim": head, "vdim": 2 * head, "tau": 16.0}
+    lat = {"heads": heads, "dim": head, "rot_dim": 48, "vdim": head, "kv_rank": 80, "scale": (head + 48) ** -0.5,
+           "rot": {"dims": 48, "base": 1000000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
+    cycle = [("attention", att, dense), ("gla", lin, moe), ("latent_attention", lat, moe), ("attention", att, moe),
+             ("attention", att, moe), ("gla", lin, moe)]
+    return {"architecture": "Kebesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (cycle[i % 6] for i in range(n_layers))]}
+
+
 PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-a": dict(_QWEN2, hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
                    num_key_value_heads=2, head_dim=16, vocab_size=512, max_position_embeddings=256, rope_theta=10000.0,
@@ -60,6 +79,10 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "mepolix-w896": _mepolix(896, 4864, 14, 2, 64, 24, 151936),
     "mepolix-w1536": _mepolix(1536, 8960, 12, 2, 128, 28, 151936),
     "mepolix-w3584": _mepolix(3584, 18944, 28, 4, 128, 28, 152064),
+    # the Kebesun design at the same widths (see `_kebesun`)
+    "kebesun-w896": _kebesun(896, 4864, 14, 2, 64, 24, 151936),
+    "kebesun-w1536": _kebesun(1536, 8960, 12, 2, 128, 24, 151936),
+    "kebesun-w3584": _kebesun(3584, 18944, 28, 4, 128, 24, 152064),
 }
 
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
@@ -335,7 +358,11 @@ def model_prefill_flops(model, lengths: Sequence[int]) -> float:
                 if isinstance(v, Linear):
                     total += 2.0 * T * v.weight.numel()
             if isinstance(part, GQAttention):
-                total += part.H * 2.0 * squares * part.hd
+                # a window bounds the keys a row reads
+                w = getattr(part, "window", None)
+                total += part.H * 2.0 * part.hd * (squares if not w else sum(float(n) * min(n, 2 * w) for n in lengths))
+            if hasattr(part, "flops_per_token"):
+                total += T * part.flops_per_token()
     return total + 2.0 * model.config.vocab_size * model.parts.head.hidden * len(lengths)
 
 

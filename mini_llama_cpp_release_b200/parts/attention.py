@@ -163,14 +163,14 @@ class GQAttention(Part):
         window = self.window or 0
         keep = getattr(self, "keep_first", 0) if window else 0     # first keys that stay visible beside the window
         sinks = getattr(self, "sinks", None)          # float32 [heads] or None: a logit per head that joins every softmax
-        if self.use_tensor_cores and not keep:
+        if self.use_tensor_cores:
             row_tiles, n_splits = kernels.attention_mma_plan(step.max_q_len, step.n_seqs, step.max_kv_len, self.H,
                                                              self.KV, rt.n_sms)
             if (step.max_q_len >= 16 and n_splits == 1
                     and kernels.attention_tcgen05_takes(self.hd, kv.page_size, self.H, self.KV)):
                 # prompts whose rows fill the GPU without sharing out the keys: the tcgen05 kernel
                 kernels.attention_tcgen05(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                                          self.scale, window, sinks=sinks)
+                                          self.scale, window, sinks=sinks, keep_first=keep)
                 return
             part_ml = part_o = None
             if step.max_q_len == 1 and row_tiles == 1:
@@ -181,7 +181,7 @@ class GQAttention(Part):
                 part_ml = rt.empty(q.shape[0] * self.H * n_splits * 2, dtype=torch.float32)
                 part_o = rt.empty(q.shape[0] * self.H * n_splits * self.hd, dtype=torch.float32)
             kernels.attention_mma(q, o, step.cu_seqlens, step.start_pos, step.n_seqs, step.max_q_len, self.H, kv,
-                                  self.scale, window, row_tiles, n_splits, part_ml, part_o, sinks=sinks)
+                                  self.scale, window, row_tiles, n_splits, part_ml, part_o, sinks=sinks, keep_first=keep)
             return
         n_splits = choose_splits(step, self.H, self.KV, rt.n_sms, tokens_per_block=max(1, 16 // min(16, self.H // self.KV)))
         part_ml = part_o = None
@@ -396,6 +396,10 @@ class LatentAttention(GQAttention):
     def weight_bytes(self) -> int:
         return (self.in_proj.nbytes() + self.o.nbytes()
                 + sum(w.numel() * w.element_size() for w in (self.w_uk, self.w_uv)))
+
+    def flops_per_token(self) -> float:
+        """Multiply-adds x 2 of the two per-head expansions."""
+        return 2.0 * self.H * self.rank * (self.dim + self.vdim)
 
     def forward(self, h: torch.Tensor, step, memory: MixerMemory, residual: Optional[torch.Tensor] = None):
         rt = self.runtime

@@ -126,6 +126,10 @@ class MixtureOfExperts(Part):
         return (self.gate_up.numel() * self.gate_up.element_size() + self.down.numel() * self.down.element_size()
                 + self.router.numel() * 4)
 
+    def flops_per_token(self) -> float:
+        """Multiply-adds x 2 a token costs: the router and `top` experts."""
+        return 2.0 * (self.E * self.hidden + self.top * 3 * self.inter * self.hidden)
+
     def route(self, h: torch.Tensor):
         """(ids int32 [n, top], weights float32 [n, top])."""
         rt = self.runtime

@@ -91,6 +91,8 @@ def frequencies(rot: dict):
 def rotate(x: torch.Tensor, positions: torch.Tensor, rot: dict) -> torch.Tensor:
     """x [T, heads, d]; the first rot.dims entries of each head turn, entry i with entry i + dims/2.  The angle is the
     float32 product of the position and the float32 frequency."""
+    if not rot or not int(rot.get("dims", 0)):
+        return x
     dims = int(rot["dims"])
     f, m = frequencies(rot)
     angle = (positions.to(torch.float32)[:, None] * f.to(torch.float32)[None, :]).to(x.dtype)
@@ -127,8 +129,8 @@ def softmax_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: 
 def window_attention(h, w, p, m, positions):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = rotate((h @ w[p + "q"].t()).view(T, H, d), positions, m["rot"])
-    k = rotate((h @ w[p + "k"].t()).view(T, G, d), positions, m["rot"])
+    q = rotate((h @ w[p + "q"].t()).view(T, H, d), positions, m.get("rot"))
+    k = rotate((h @ w[p + "k"].t()).view(T, G, d), positions, m.get("rot"))
     v = (h @ w[p + "v"].t()).view(T, G, dv)
     mask = m.get("mask") or {}
     o = softmax_attention(q, k, v, float(m["scale"]), visible(T, mask.get("size"), int(mask.get("keep_first", 0))))
