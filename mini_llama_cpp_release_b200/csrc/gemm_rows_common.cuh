@@ -27,6 +27,10 @@ struct RowsArgs {
     int rope_positions;
     int q_heads, kv_heads, hd;
     PagedKV cache;
+    // grouped form (one-SM kernel only): every token tile of 128 rows multiplies by the matrix of its own group, group e's
+    // n_out rows starting at row e * n_out of W.  tile_group [m_tiles]: the tile's group, negative: the tile is skipped.
+    // The table comes from a kernel before this one, so nothing is asked for ahead of the wait for that kernel.
+    const int* tile_group;
 };
 
 constexpr int R_BM = 128;

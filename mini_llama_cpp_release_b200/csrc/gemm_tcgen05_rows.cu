@@ -66,6 +66,9 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     auto tile_n0 = [&](int t) { return ((t / g.m_tiles) % g.n_tiles) * BN; };
     auto tile_kb0 = [&](int t) { return (t / (g.m_tiles * g.n_tiles)) * g.k_blocks_per_split; };       // first K block of the tile's share
     auto tile_nkb = [&](int t) { return min(g.k_blocks, tile_kb0(t) + g.k_blocks_per_split) - tile_kb0(t); };
+    const bool grouped = g.tile_group != nullptr;
+    // the group of tile t's tokens (0 when the product is not grouped); a negative group: no role touches the tile
+    auto tile_grp = [&](int t) { return grouped ? __ldg(g.tile_group + t % g.m_tiles) : 0; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) {
@@ -94,10 +97,13 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (lane == 0) {
             int it = 0;
             bool alive = true;
+            if (grouped) grid_dependency_wait();
             for (int t = blockIdx.x; t < n_tiles_total && alive; t += gridDim.x) {
-                const int m0 = tile_m0(t), n0 = tile_n0(t), kb0 = tile_kb0(t), n_kb = tile_nkb(t);
+                const int grp = tile_grp(t);
+                if (grp < 0) continue;
+                const int m0 = tile_m0(t), n0 = tile_n0(t) + grp * g.n_out, kb0 = tile_kb0(t), n_kb = tile_nkb(t);
                 int i = 0;
-                if (it == 0) {
+                if (it == 0 && !grouped) {
                     const int early = min(n_kb, S::STAGES);
                     for (; i < early; ++i) {
                         mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
@@ -123,7 +129,9 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             constexpr unsigned idesc = umma_idesc(BN);
             int it = 0, j = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
+            if (grouped) grid_dependency_wait();
+            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
+                if (tile_grp(t) < 0) continue;
                 const int buf = j & 1;
                 ok = mbar_wait(acc_empty_bar(buf), (((unsigned)j >> 1) & 1u) ^ 1u, g.status, 22);
                 if (!ok) break;
@@ -145,6 +153,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 }
                 if (!ok) break;
                 tcgen05_commit(acc_full_bar(buf));
+                ++j;
             }
         }
     } else {
@@ -155,7 +164,8 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         grid_dependency_wait();                // positions, page lists and the output may come from earlier kernels
         int j = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++j) {
+        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
+            if (tile_grp(t) < 0) continue;
             const int m0 = tile_m0(t), n0 = tile_n0(t);
             const int buf = j & 1;
             const int tok = m0 + q * 32 + lane;
@@ -245,6 +255,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // the accumulator has been read: the tensor cores may fill it again
             tcgen05_fence_before();
             mbar_arrive(acc_empty_bar(buf));
+            ++j;
         }
     }
 
@@ -344,4 +355,38 @@ extern "C" int mlc_gemm_tcgen05_rows(const void* x, const void* w, void* out, in
     if (epilogue == R_EPI_QKV) return block_rows == 128 ? launch_rows<128, R_EPI_QKV>(mx, mw, g, n_sms, s) : MLC_ERR_BAD_SIZE;
     if (epilogue == R_EPI_ADD) return dispatch_rows<R_EPI_ADD>(block_rows, mx, mw, g, n_sms, s);
     return MLC_ERR_UNSUPPORTED;
+}
+
+// The grouped form: x bfloat16 [n_rows][K], n_rows a multiple of 128, every tile of 128 rows belonging to one group;
+// w bfloat16 [n_groups * n_out][K], group e's matrix in rows e * n_out on; tile_group int32 [n_rows / 128] on the device
+// (negative: the tile holds no rows and is skipped).  Epilogues 0 (out [n_rows][n_out] float32 or bfloat16) and 1
+// (gate and up rows interleaved, out [n_rows][n_out / 2]).  Status codes as above.
+extern "C" int mlc_gemm_tcgen05_rows_grouped(const void* x, const void* w, void* out, int out_dtype, int n_rows, int n_out, int K,
+                                             int block_rows, int epilogue, int* status, int n_sms, const int* tile_group,
+                                             int n_groups, void* stream) {
+    if (n_rows <= 0 || n_out <= 0) return 0;
+    if (K <= 0 || (K & 7) || (n_out & 15) || (n_rows % R_BM) || (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return MLC_ERR_BAD_SIZE;
+    if (out_dtype != MLC_DTYPE_F32 && out_dtype != MLC_DTYPE_BF16) return MLC_ERR_BAD_DTYPE;
+    if (status == nullptr || n_sms < 1 || tile_group == nullptr || n_groups < 1) return MLC_ERR_BAD_SIZE;
+    if (epilogue != R_EPI_STORE && epilogue != R_EPI_SILU_MUL) return MLC_ERR_UNSUPPORTED;
+    RowsArgs g{};
+    g.out = out;
+    g.out_dtype = out_dtype;
+    g.n_out = n_out;
+    g.n_tok = n_rows;
+    g.k_blocks = (K + R_BK - 1) / R_BK;
+    g.m_tiles = n_rows / R_BM;
+    g.n_tiles = (n_out + block_rows - 1) / block_rows;
+    g.n_splits = 1;
+    g.k_blocks_per_split = g.k_blocks;
+    g.status = status;
+    g.tile_group = tile_group;
+    CUtensorMap mx, mw;
+    int rc = rows_map(&mx, x, n_rows, K, R_BM);
+    if (rc) return rc;
+    rc = rows_map(&mw, w, (long long)n_groups * n_out, K, block_rows);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (epilogue == R_EPI_STORE) return dispatch_rows<R_EPI_STORE>(block_rows, mx, mw, g, n_sms, s);
+    return dispatch_rows<R_EPI_SILU_MUL>(block_rows, mx, mw, g, n_sms, s);
 }

@@ -6,25 +6,28 @@
 // The state starts at zero, lives in float32 and is carried per sequence in a slot's row; decays, their logarithms
 // and everything else that enters the recurrence are float32 whatever the engine's type.
 //
-// The walk: a block owns (sequence, head, 32 columns of S).  Eight neighbouring lanes share a column and hold every
-// eighth row of it in registers; tokens arrive sixteen at a time through shared memory (q scaled, k, the decays
-// already exponentiated), so the dependent chain per token is one multiply-add per held row, one more for the
-// output, and three shuffles.  State layout in a slot's row: [head][column][row] (a column's rows side by side).
+// Two kernels.  The first turns every decay logit into its decay in place, all tokens and channels at once.  The second
+// walks: a block owns (sequence, head, 16 columns of S); a thread holds two columns x an eighth of the rows (side by
+// side) in registers.  Tokens arrive sixteen at a time through shared memory while the next sixteen are on their way
+// from memory into registers, and are walked four at a time: a row's state takes one multiply-add per token, and the
+// four tokens' output sums, with their three shuffles each, are independent of one another and overlap; their results
+// are stored behind the group.  The small blocks are many (heads x vdim / 16 per sequence), so that a prompt of one
+// sequence still spreads over the GPU.  Tokens that are not there count as q = k = v = 0 with a
+// decay of one.  State layout in a slot's row: [head][column][row] (a column's rows side by side).
 #include "common.cuh"
 
 namespace mlc {
 
-constexpr int GLA_COLS = 32;       // columns of S per block
-constexpr int GLA_SPLIT = 8;       // lanes per column
 constexpr int GLA_CHUNK = 16;      // tokens staged at a time
+constexpr int GLA_COLS = 16;       // columns of S per block
+constexpr int GLA_THREADS = 64;    // 8 pairs of columns x 8 groups of rows
+constexpr int GLA_V_LOADS = GLA_CHUNK * GLA_COLS / GLA_THREADS;
 
 struct GlaArgs {
     const float* proj;          // rows of the input product
     long long proj_stride;
     int q_col, k_col, v_col;
-    const float* z;             // [n][H*dim] decay logits without their bias
-    const float* z_bias;        // [H*dim] or null
-    float inv_tau;
+    const float* decay;         // [n][H*dim] decays
     float q_scale;
     float* state;               // [slots][H*vdim*dim]
     long long state_stride;
@@ -34,76 +37,146 @@ struct GlaArgs {
     int H, dim, vdim;
 };
 
-__device__ __forceinline__ float decay_of(float z, float inv_tau) {
-    // logsigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-    const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
-    return expf(ls * inv_tau);
+// z <- sigmoid(z + bias)^(1/tau) = exp(logsigmoid(z + bias) / tau),  logsigmoid(x) = min(x, 0) - log1p(exp(-|x|))
+__global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict__ bias, long long total, int width, float inv_tau) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const float x = z[idx] + (bias != nullptr ? bias[idx % width] : 0.0f);
+    z[idx] = expf((fminf(x, 0.0f) - log1pf(expf(-fabsf(x)))) * inv_tau);
 }
 
-template <int ROWS>       // rows of a column one lane holds: dim <= 8 * ROWS
-__global__ void __launch_bounds__(GLA_COLS * GLA_SPLIT)
+template <int ROWS>       // rows of a column one thread holds, side by side: dim <= DP = 8 * ROWS
+__global__ void __launch_bounds__(GLA_THREADS)
 gla_walk_kernel(GlaArgs a) {
-    extern __shared__ float sh[];
+    constexpr int DP = 8 * ROWS;
+    constexpr int U = GLA_CHUNK * DP / GLA_THREADS;  // q, k, decay logits a thread brings per chunk
+    extern __shared__ __align__(16) float sh[];
+    float* qs = sh;                                  // [CHUNK][DP] q · dim^-1/2
+    float* ks = qs + GLA_CHUNK * DP;                 // [CHUNK][DP]
+    float* as = ks + GLA_CHUNK * DP;                 // [CHUNK][DP] decays
+    float* vs = as + GLA_CHUNK * DP;                 // [CHUNK][COLS]
     const int dim = a.dim, vdim = a.vdim;
-    float* qs = sh;                                  // [CHUNK][dim]
-    float* ks = qs + GLA_CHUNK * dim;
-    float* as = ks + GLA_CHUNK * dim;
-    float* vs = as + GLA_CHUNK * dim;                // [CHUNK][GLA_COLS]
     const int head = blockIdx.x, seq = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
-    const int r = threadIdx.x % GLA_SPLIT, c = threadIdx.x / GLA_SPLIT;
-    const int col = col0 + c;
-    const bool col_ok = col < vdim;
+    const int tid = threadIdx.x;
+    const int r = tid & 7, cp = tid >> 3;
+    const int col = col0 + 2 * cp;
     const int t0 = a.cu_seqlens[seq], t1 = a.cu_seqlens[seq + 1];
-    float* S_row = a.state + (long long)a.slots[seq] * a.state_stride + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
-    float S[ROWS];
+    float* S_base = a.state + (long long)a.slots[seq] * a.state_stride + (long long)head * vdim * dim;
+    float S[2][ROWS];
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-        const int row = i * GLA_SPLIT + r;
-        S[i] = (col_ok && row < dim) ? S_row[row] : 0.0f;
-    }
-    for (int c0 = t0; c0 < t1; c0 += GLA_CHUNK) {
-        const int n_here = min(GLA_CHUNK, t1 - c0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < n_here * dim; idx += blockDim.x) {
-            const int tt = idx / dim, d = idx % dim;
-            const float* row = a.proj + (long long)(c0 + tt) * a.proj_stride;
-            qs[idx] = row[a.q_col + head * dim + d] * a.q_scale;
-            ks[idx] = row[a.k_col + head * dim + d];
-            const int zc = head * dim + d;
-            as[idx] = decay_of(a.z[(long long)(c0 + tt) * a.H * dim + zc] + (a.z_bias != nullptr ? a.z_bias[zc] : 0.0f), a.inv_tau);
-        }
-        for (int idx = threadIdx.x; idx < n_here * GLA_COLS; idx += blockDim.x) {
-            const int tt = idx / GLA_COLS, cc = idx % GLA_COLS;
-            vs[idx] = (col0 + cc < vdim) ? a.proj[(long long)(c0 + tt) * a.proj_stride + a.v_col + head * vdim + col0 + cc] : 0.0f;
-        }
-        __syncthreads();
-        for (int tt = 0; tt < n_here; ++tt) {
-            const float v = vs[tt * GLA_COLS + c];
-            const float* q = qs + tt * dim;
-            const float* k = ks + tt * dim;
-            const float* al = as + tt * dim;
-            float acc = 0.0f;
-#pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int row = i * GLA_SPLIT + r;
-                if (row < dim) {
-                    S[i] = fmaf(al[row], S[i], k[row] * v);
-                    acc = fmaf(S[i], q[row], acc);
-                }
-            }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (r == 0 && col_ok) a.out[(long long)(c0 + tt) * a.H * vdim + head * vdim + col] = acc;
-        }
-    }
-    if (col_ok) {
+    for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
-            const int row = i * GLA_SPLIT + r;
-            if (row < dim) S_row[row] = S[i];
+            const int row = r * ROWS + i;
+            S[c][i] = (col + c < vdim && row < dim) ? S_base[(long long)(col + c) * dim + row] : 0.0f;
+        }
+
+    float rq[U], rk[U], ra[U], rv[GLA_V_LOADS];
+    auto fetch = [&](int c0) {
+        const int n_here = min(GLA_CHUNK, t1 - c0);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = tid + u * GLA_THREADS;
+            const int tt = idx / DP, d = idx % DP;
+            rq[u] = rk[u] = 0.0f;
+            ra[u] = 1.0f;                             // no token, or no such channel: a decay of one, q and k zero
+            if (tt < n_here && d < dim) {
+                const float* row = a.proj + (long long)(c0 + tt) * a.proj_stride + head * dim + d;
+                rq[u] = row[a.q_col];
+                rk[u] = row[a.k_col];
+                ra[u] = a.decay[(long long)(c0 + tt) * a.H * dim + head * dim + d];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < GLA_V_LOADS; ++u) {
+            const int idx = tid + u * GLA_THREADS;
+            const int tt = idx / GLA_COLS, cc = idx % GLA_COLS;
+            rv[u] = (tt < n_here && col0 + cc < vdim) ? a.proj[(long long)(c0 + tt) * a.proj_stride + a.v_col + head * vdim + col0 + cc] : 0.0f;
+        }
+    };
+    if (t0 < t1) fetch(t0);
+    for (int c0 = t0; c0 < t1; c0 += GLA_CHUNK) {
+        const int n_here = min(GLA_CHUNK, t1 - c0);
+        __syncthreads();                              // the chunk before has been read
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = tid + u * GLA_THREADS;
+            qs[idx] = rq[u] * a.q_scale;
+            ks[idx] = rk[u];
+            as[idx] = ra[u];
+        }
+#pragma unroll
+        for (int u = 0; u < GLA_V_LOADS; ++u) vs[tid + u * GLA_THREADS] = rv[u];
+        __syncthreads();
+        if (c0 + GLA_CHUNK < t1) fetch(c0 + GLA_CHUNK);       // in flight while this chunk is walked
+        // groups of four tokens (a single token, a decode step, is a group of one)
+        const int group = n_here == 1 ? 1 : 4;
+        for (int g0 = 0; g0 < n_here; g0 += group) {
+            float res0[4], res1[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (u >= group) break;
+                const int t = g0 + u;
+                const float2 v2 = *reinterpret_cast<const float2*>(vs + t * GLA_COLS + 2 * cp);
+                const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP + r * ROWS);
+                const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP + r * ROWS);
+                const float4* a4 = reinterpret_cast<const float4*>(as + t * DP + r * ROWS);
+                float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+                for (int i4 = 0; i4 < ROWS / 4; ++i4) {
+                    const float4 q = q4[i4], k = k4[i4], al = a4[i4];
+                    const float qv[4] = {q.x, q.y, q.z, q.w}, kv[4] = {k.x, k.y, k.z, k.w}, av[4] = {al.x, al.y, al.z, al.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        S[0][4 * i4 + e] = fmaf(av[e], S[0][4 * i4 + e], kv[e] * v2.x);
+                        S[1][4 * i4 + e] = fmaf(av[e], S[1][4 * i4 + e], kv[e] * v2.y);
+                        acc0 = fmaf(S[0][4 * i4 + e], qv[e], acc0);
+                        acc1 = fmaf(S[1][4 * i4 + e], qv[e], acc1);
+                    }
+                }
+                res0[u] = acc0;
+                res1[u] = acc1;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (u >= group) break;
+                res0[u] += __shfl_xor_sync(0xffffffffu, res0[u], 1); res1[u] += __shfl_xor_sync(0xffffffffu, res1[u], 1);
+                res0[u] += __shfl_xor_sync(0xffffffffu, res0[u], 2); res1[u] += __shfl_xor_sync(0xffffffffu, res1[u], 2);
+                res0[u] += __shfl_xor_sync(0xffffffffu, res0[u], 4); res1[u] += __shfl_xor_sync(0xffffffffu, res1[u], 4);
+            }
+            if (r == 0) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (u >= group || g0 + u >= n_here) break;
+                    float* o = a.out + (long long)(c0 + g0 + u) * a.H * vdim + head * vdim + col;
+                    if (col < vdim) o[0] = res0[u];
+                    if (col + 1 < vdim) o[1] = res1[u];
+                }
+            }
         }
     }
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int row = r * ROWS + i;
+            if (col + c < vdim && row < dim) S_base[(long long)(col + c) * dim + row] = S[c][i];
+        }
+}
+
+template <int ROWS>
+static int launch_gla(const GlaArgs& a, dim3 grid, cudaStream_t s) {
+    constexpr int DP = 8 * ROWS;
+    const size_t smem = (size_t)(3 * GLA_CHUNK * DP + GLA_CHUNK * GLA_COLS) * sizeof(float);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        cudaError_t e = cudaFuncSetAttribute(gla_walk_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    gla_walk_kernel<ROWS><<<grid, GLA_THREADS, smem, s>>>(a);
+    MLC_LAUNCH_CHECK();
+    return 0;
 }
 
 }  // namespace mlc
@@ -111,33 +184,23 @@ gla_walk_kernel(GlaArgs a) {
 using namespace mlc;
 
 // proj: float32 rows (stride proj_stride) holding q (H x dim) at q_col, k (H x dim) at k_col, v (H x vdim) at v_col.
-// z: float32 [n][H*dim] decay logits, z_bias [H*dim] or null.  state: float32, a slot's row holds H*vdim*dim floats.
+// z: float32 [n][H*dim] decay logits (overwritten with the decays), z_bias [H*dim] or null.  state: float32, a slot's row holds H*vdim*dim floats.
 // out: float32 [n][H*vdim].
-extern "C" int mlc_gla(const float* proj, long long proj_stride, int q_col, int k_col, int v_col, const float* z,
+extern "C" int mlc_gla(const float* proj, long long proj_stride, int q_col, int k_col, int v_col, float* z,
                        const float* z_bias, float tau, float* state, long long state_stride, const int* slots,
                        const int* cu_seqlens, int n_seqs, int n_tokens, int H, int dim, int vdim, float* out, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (H <= 0 || dim <= 0 || dim > 256 || vdim <= 0 || !(tau > 0.0f) || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
-    GlaArgs a{proj, proj_stride, q_col, k_col, v_col, z, z_bias, 1.0f / tau, 1.0f / sqrtf((float)dim), state, state_stride,
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)n_tokens * H * dim;
+    gla_decay_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(z, z_bias, total, H * dim, 1.0f / tau);
+    MLC_LAUNCH_CHECK();
+    GlaArgs a{proj, proj_stride, q_col, k_col, v_col, z, 1.0f / sqrtf((float)dim), state, state_stride,
               slots, cu_seqlens, out, H, dim, vdim};
     const dim3 grid(H, n_seqs, (vdim + GLA_COLS - 1) / GLA_COLS);
-    const size_t smem = (size_t)(3 * GLA_CHUNK * dim + GLA_CHUNK * GLA_COLS) * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
-    if (dim <= 32)
-        gla_walk_kernel<4><<<grid, GLA_COLS * GLA_SPLIT, smem, s>>>(a);
-    else if (dim <= 64)
-        gla_walk_kernel<8><<<grid, GLA_COLS * GLA_SPLIT, smem, s>>>(a);
-    else if (dim <= 128)
-        gla_walk_kernel<16><<<grid, GLA_COLS * GLA_SPLIT, smem, s>>>(a);
-    else {
-        static bool raised = false;                // 16 tokens of 3 x 256 floats pass the default 48 KB
-        if (!raised) {
-            cudaError_t e = cudaFuncSetAttribute(gla_walk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-            if (e != cudaSuccess) return (int)e;
-            raised = true;
-        }
-        gla_walk_kernel<32><<<grid, GLA_COLS * GLA_SPLIT, smem, s>>>(a);
-    }
-    MLC_LAUNCH_CHECK();
-    return 0;
+    if (dim <= 32) return launch_gla<4>(a, grid, s);
+    if (dim <= 64) return launch_gla<8>(a, grid, s);
+    if (dim <= 128) return launch_gla<16>(a, grid, s);
+    return launch_gla<32>(a, grid, s);
 }
+

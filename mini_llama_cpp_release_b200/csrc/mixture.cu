@@ -18,16 +18,51 @@ namespace mlc {
 
 constexpr int ROUTE_MAX_PER_LANE = 8;          // E <= 256
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int n, int E, int top,
-                                 int* __restrict__ ids, float* __restrict__ weights) {
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= n) return;
-    const int lane = threadIdx.x & 31;
+// A block of four warps per token.  With `w` given, `x` is the branch's input [n][K] (TX) and the logits are
+// x · wᵀ + bias in float32 (w float32 [E][K]): eight experts at a time, every thread a strided share of K, partial sums
+// added within warps and then across them in a fixed order.  Without `w`, `x` holds the logits themselves, float32 [n][E].
+// Warp 0 then chooses: lane l keeps logits l, l + 32, ...
+template <typename TX>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int n,
+                 int E, int K, int top, int* __restrict__ ids, float* __restrict__ weights) {
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float part[4][8];
+    __shared__ float logit[32 * ROUTE_MAX_PER_LANE];
+    if (w != nullptr) {
+        const TX* row = x + (long long)t * K;
+        for (int e0 = 0; e0 < E; e0 += 8) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 4
+            for (int k = threadIdx.x; k < K; k += 128) {
+                const float xv = to_float(row[k]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(xv, __ldg(w + (long long)min(e0 + j, E - 1) * K + k), acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float v = warp_sum(acc[j]);
+                if (lane == 0) part[warp][j] = v;
+            }
+            __syncthreads();
+            if (threadIdx.x < 8 && e0 + threadIdx.x < E) {
+                const int e = e0 + threadIdx.x;
+                logit[e] = ((part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]))
+                           + (bias != nullptr ? bias[e] : 0.0f);
+            }
+            __syncthreads();
+        }
+    }
+    if (warp != 0) return;
     float z[ROUTE_MAX_PER_LANE];
 #pragma unroll
     for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k) {
         const int e = lane + 32 * k;
-        z[k] = e < E ? logits[(long long)t * E + e] + (bias != nullptr ? bias[e] : 0.0f) : -INFINITY;
+        z[k] = -INFINITY;
+        if (e < E) z[k] = w != nullptr ? logit[e] : reinterpret_cast<const float*>(x)[(long long)t * E + e] + (bias != nullptr ? bias[e] : 0.0f);
     }
     float mine = -INFINITY;          // lane j keeps the j-th chosen logit
     float first = 0.0f;
@@ -51,7 +86,11 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
                 where = ow;
             }
         }
-        if (where != 0x7fffffff && (where & 31) == lane) z[where >> 5] = -INFINITY;
+        if (where != 0x7fffffff && (where & 31) == lane) {
+#pragma unroll
+            for (int k = 0; k < ROUTE_MAX_PER_LANE; ++k)
+                if (k == (where >> 5)) z[k] = -INFINITY;
+        }
         if (lane == j) mine = best;
         if (j == 0) first = best;                     // the largest: the softmax's reference point
         if (lane == 0) ids[(long long)t * top + j] = where == 0x7fffffff ? 0 : where;
@@ -61,47 +100,61 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
     if (lane < top) weights[(long long)t * top + lane] = p / sum;
 }
 
-// One block.  Shared: counts and offsets per expert.
+// One block of 32 warps.  Warp w takes the w-th stretch of the pairs.  Shared: cnt[w][e], the pairs of expert e in
+// stretch w, turned into the row at which stretch w's pairs of expert e begin; inside a stretch the pairs of an expert
+// keep their order (lanes that hold the same expert find each other with match.any), so an expert's rows are its pairs in
+// pair order, whatever the number of warps.
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int top, int E, int tile, int max_rows, int* __restrict__ row_of,
                 int* __restrict__ src_tok, int* __restrict__ tile_expert) {
     extern __shared__ int sh[];
-    int* cnt = sh;             // [E]
-    int* off = sh + E;         // [E]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    for (int e = warp; e < E; e += n_warps) {
-        int c = 0;
-        for (int p = lane; p < n_pairs; p += 32) c += ids[p] == e;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-        if (lane == 0) cnt[e] = c;
-    }
+    int* cnt = sh;                 // [32][E]
+    int* start = sh + 32 * E;      // [E]: first row of the expert's run
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per = ((n_pairs + 31) / 32 + 31) / 32 * 32;            // pairs per stretch, a multiple of 32
+    const int p_begin = min(n_pairs, warp * per), p_end = min(n_pairs, p_begin + per);
+    for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) cnt[i] = 0;
     for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_tok[r] = -1;
     for (int t = threadIdx.x; t < max_rows / tile; t += blockDim.x) tile_expert[t] = -1;
+    __syncthreads();
+    for (int p0 = p_begin; p0 < p_end; p0 += 32) {
+        const int p = p0 + lane;
+        const bool have = p < p_end;
+        const int e = have ? ids[p] : -1 - lane;                     // lanes without a pair match nobody
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (have && (same & ((1u << lane) - 1u)) == 0) cnt[warp * E + e] += __popc(same);      // the first lane of each expert
+        __syncwarp();
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
         for (int e = 0; e < E; ++e) {
-            off[e] = at;
-            const int tiles = (cnt[e] + tile - 1) / tile;
+            start[e] = at;
+            int c = 0;
+            for (int w = 0; w < 32; ++w) {
+                const int here = cnt[w * E + e];
+                cnt[w * E + e] = at + c;
+                c += here;
+            }
+            const int tiles = (c + tile - 1) / tile;
             for (int t = 0; t < tiles; ++t) tile_expert[at / tile + t] = e;
             at += tiles * tile;
         }
     }
     __syncthreads();
-    for (int e = warp; e < E; e += n_warps) {
-        int base = off[e];
-        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
-            const int p = p0 + lane;
-            const bool hit = p < n_pairs && ids[p] == e;
-            const unsigned mask = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                const int row = base + __popc(mask & ((1u << lane) - 1u));
-                row_of[p] = row;
-                src_tok[row] = p / top;
-            }
-            base += __popc(mask);
+    for (int p0 = p_begin; p0 < p_end; p0 += 32) {
+        const int p = p0 + lane;
+        const bool have = p < p_end;
+        const int e = have ? ids[p] : -1 - lane;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (have) {
+            const int row = cnt[warp * E + e] + __popc(same & ((1u << lane) - 1u));
+            row_of[p] = row;
+            src_tok[row] = p / top;
         }
+        __syncwarp();
+        if (have && (same & ((1u << lane) - 1u)) == 0) cnt[warp * E + e] += __popc(same);
+        __syncwarp();
     }
 }
 
@@ -184,32 +237,59 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     }
 }
 
-// x[t][i] += s1[i] · sum_slices y1[.][t][i] (+ s2[i] · sum_slices y2[.][t][i]); a null factor is one
+// x[t][i] += s1[i] · sum_slices y1[.][t][i] (+ s2[i] · sum_slices y2[.][t][i]); a null factor is one.  VEC floats a thread.
+template <int VEC>
 __global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ y1, int slices1, const float* __restrict__ s1,
                                   const float* __restrict__ y2, int slices2, const float* __restrict__ s2, long long total, int d) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (idx >= total) return;
     const int i = (int)(idx % d);
-    float a = 0.0f;
-    for (int s = 0; s < slices1; ++s) a += y1[(long long)s * total + idx];
-    float v = x[idx] + (s1 != nullptr ? s1[i] * a : a);
-    if (y2 != nullptr) {
-        float b = 0.0f;
-        for (int s = 0; s < slices2; ++s) b += y2[(long long)s * total + idx];
-        v += s2 != nullptr ? s2[i] * b : b;
+    float a[VEC], b[VEC], v[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) a[e] = b[e] = 0.0f;
+    if (VEC == 4) {
+        for (int s = 0; s < slices1; ++s) {
+            const float4 t = *reinterpret_cast<const float4*>(y1 + (long long)s * total + idx);
+            a[0] += t.x; a[1 % VEC] += t.y; a[2 % VEC] += t.z; a[3 % VEC] += t.w;
+        }
+        if (y2 != nullptr)
+            for (int s = 0; s < slices2; ++s) {
+                const float4 t = *reinterpret_cast<const float4*>(y2 + (long long)s * total + idx);
+                b[0] += t.x; b[1 % VEC] += t.y; b[2 % VEC] += t.z; b[3 % VEC] += t.w;
+            }
+        const float4 t = *reinterpret_cast<const float4*>(x + idx);
+        v[0] = t.x; v[1 % VEC] = t.y; v[2 % VEC] = t.z; v[3 % VEC] = t.w;
+    } else {
+        for (int s = 0; s < slices1; ++s) a[0] += y1[(long long)s * total + idx];
+        if (y2 != nullptr)
+            for (int s = 0; s < slices2; ++s) b[0] += y2[(long long)s * total + idx];
+        v[0] = x[idx];
     }
-    x[idx] = v;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        v[e] += s1 != nullptr ? s1[i + e] * a[e] : a[e];
+        if (y2 != nullptr) v[e] += s2 != nullptr ? s2[i + e] * b[e] : b[e];
+    }
+    if (VEC == 4) *reinterpret_cast<float4*>(x + idx) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+    else x[idx] = v[0];
 }
 
 }  // namespace mlc
 
 using namespace mlc;
 
-extern "C" int mlc_moe_route(const float* logits, const float* bias, int n, int E, int top, int* ids, float* weights,
-                             void* stream) {
+// x: with w, the branch's input [n][K] of x_dtype (w float32 [E][K]); without w, the logits float32 [n][E] (K unused).
+extern "C" int mlc_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int n, int E, int K, int top,
+                             int* ids, float* weights, void* stream) {
     if (n <= 0) return 0;
-    if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > 32 || top > E) return MLC_ERR_BAD_SIZE;
-    moe_route_kernel<<<(n + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits, bias, n, E, top, ids, weights);
+    if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE || top <= 0 || top > 32 || top > E || (w != nullptr && K <= 0)) return MLC_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w == nullptr || x_dtype == MLC_DTYPE_F32)
+        moe_route_kernel<float><<<n, 128, 0, s>>>((const float*)x, w, bias, n, E, K, top, ids, weights);
+    else if (x_dtype == MLC_DTYPE_BF16)
+        moe_route_kernel<bf16><<<n, 128, 0, s>>>((const bf16*)x, w, bias, n, E, K, top, ids, weights);
+    else
+        return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();
     return 0;
 }
@@ -217,11 +297,11 @@ extern "C" int mlc_moe_route(const float* logits, const float* bias, int n, int 
 extern "C" int mlc_moe_plan(const int* ids, int n_pairs, int top, int E, int tile, int max_rows, int* row_of, int* src_tok,
                             int* tile_expert, void* stream) {
     if (n_pairs <= 0) return 0;
-    if (E <= 0 || E > 4096 || tile <= 0 || max_rows % tile != 0 || top <= 0) return MLC_ERR_BAD_SIZE;
+    if (E <= 0 || E > 256 || tile <= 0 || max_rows % tile != 0 || top <= 0) return MLC_ERR_BAD_SIZE;
     // every expert's run, rounded up to whole tiles, must fit
     const long long most = (long long)n_pairs + (long long)(E < n_pairs ? E : n_pairs) * (tile - 1);     // only experts that were chosen have a run
     if ((long long)max_rows < most - most % tile) return MLC_ERR_BAD_SIZE;
-    moe_plan_kernel<<<1, 1024, 2 * E * sizeof(int), (cudaStream_t)stream>>>(ids, n_pairs, top, E, tile, max_rows, row_of,
+    moe_plan_kernel<<<1, 1024, 33 * E * sizeof(int), (cudaStream_t)stream>>>(ids, n_pairs, top, E, tile, max_rows, row_of,
                                                                             src_tok, tile_expert);
     MLC_LAUNCH_CHECK();
     return 0;
@@ -283,8 +363,13 @@ extern "C" int mlc_scaled_add(float* x, const float* y1, int slices1, const floa
     if (n <= 0) return 0;
     if (d <= 0 || y1 == nullptr || slices1 < 1 || (y2 != nullptr && slices2 < 1)) return MLC_ERR_BAD_SIZE;
     const long long total = n * d;
-    scaled_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, y1, slices1, s1, y2, slices2, s2,
-                                                                                         total, d);
+    const bool vec = (d & 3) == 0 && ((((uintptr_t)x) | ((uintptr_t)y1) | ((uintptr_t)y2)) & 15) == 0;
+    if (vec)
+        scaled_add_kernel<4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, y1, slices1, s1, y2, slices2,
+                                                                                                    s2, total, d);
+    else
+        scaled_add_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, y1, slices1, s1, y2, slices2, s2,
+                                                                                                total, d);
     MLC_LAUNCH_CHECK();
     return 0;
 }

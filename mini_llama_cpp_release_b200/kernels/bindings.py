@@ -18,7 +18,7 @@ __all__ = [
     "layernorm", "qk_norm_rope_cache", "softcap", "convert", "causal_conv", "gated_delta_rule", "gated_rmsnorm", "block_gates",
     "linear_scan", "gates_scan_step", "gates_scan_step_takes",
     "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "gla", "latent_prepare",
-    "head_project",
+    "head_project", "gemm_tcgen05_grouped", "GROUPED_TILE",
 ]
 
 
@@ -106,7 +106,7 @@ def core() -> ctypes.CDLL:
             "mlc_gather_rows": [P, P, I, LL, P, I, I, P, P, P],
             "mlc_convert": [P, I, LL, P, I, P],
             "mlc_attention_simt": [P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, LL, I, I, P, I, P],
-            "mlc_moe_route": [P, P, I, I, I, P, P, P],
+            "mlc_moe_route": [P, I, P, P, I, I, I, I, P, P, P],
             "mlc_moe_plan": [P, I, I, I, I, I, P, P, P, P],
             "mlc_grouped_linear": [P, I, P, P, I, P, I, I, I, I, P, I, P],
             "mlc_moe_gather": [P, I, P, I, I, P, P],
@@ -120,6 +120,7 @@ def core() -> ctypes.CDLL:
             "mlc_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_rows": [P, P, P, I, I, I, I, I, I, I, P, I, P, P, P, P, I, I, I, I, P, P, P, LL, I, I, P],
             "mlc_gemm_tcgen05_pair": [P, P, P, I, I, I, I, I, I, I, P, I, P],
+            "mlc_gemm_tcgen05_rows_grouped": [P, P, P, I, I, I, I, I, I, P, I, P, I, P],
             "mlc_copy_async": [P, P, LL, I, P],
             "mlc_argmax": [P, I, I, P, P],
             "mlc_argmax_split": [P, I, I, P, P, P, P, P],
@@ -533,15 +534,23 @@ def gates_scan_step(u: torch.Tensor, w_r_t: torch.Tensor, w_i_t: torch.Tensor, b
 
 
 # ------------------------------------------------------------------ mixture of experts (csrc/mixture.cu)
-def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
-    """Per token the `top` largest of logits + bias (float32 [n, E]; the lower index wins a tie) into ids int32 [n, top],
-    and the softmax over those chosen logits into weights float32 [n, top]."""
-    require_cuda(logits, bias, ids, weights)
-    n, E = logits.shape
-    assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
+def moe_route(x: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor,
+              router: Optional[torch.Tensor] = None) -> None:
+    """Per token the `top` largest router logits (the lower index wins a tie) into ids int32 [n, top], and the softmax over
+    those chosen logits into weights float32 [n, top].  With `router` (float32 [E, K]) x is the branch's input [n, K] and
+    the logits x · routerᵀ + bias are formed in float32 inside the kernel; without, x is the logits, float32 [n, E]."""
+    require_cuda(x, bias, ids, weights, router)
+    n = x.shape[0]
+    if router is not None:
+        E, K = router.shape
+        assert router.dtype == torch.float32 and x.shape[1] == K
+    else:
+        E, K = x.shape[1], 0
+        assert x.dtype == torch.float32
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32
     assert ids.shape == (n, top) and weights.shape == (n, top) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == E))
-    _check(core().mlc_moe_route(logits.data_ptr(), _ptr(bias), n, E, int(top), ids.data_ptr(), weights.data_ptr(), _stream()),
-           "expert routing")
+    _check(core().mlc_moe_route(x.data_ptr(), dtype_code(x.dtype), _ptr(router), _ptr(bias), n, E, K, int(top), ids.data_ptr(),
+                                weights.data_ptr(), _stream()), "expert routing")
 
 
 def moe_plan_rows(n_pairs: int, n_experts: int, tile: int) -> int:
@@ -614,8 +623,8 @@ def scaled_add(x: torch.Tensor, y1: torch.Tensor, s1: Optional[torch.Tensor], y2
 def gla(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, z_bias: Optional[torch.Tensor], tau: float,
         state: torch.Tensor, step, heads: int, dim: int, vdim: int, out: torch.Tensor) -> None:
     """S <- diag(sigmoid(z + bias)^(1/tau)) S + k vT, o = ST q dim^-1/2 over the step's tokens; q, k (heads x dim) and v
-    (heads x vdim) in the float32 rows `proj`, z float32 [n, heads*dim], state float32 [slots, heads*vdim*dim],
-    out float32 [n, heads*vdim]."""
+    (heads x vdim) in the float32 rows `proj`, z float32 [n, heads*dim] (overwritten with the decays), state float32
+    [slots, heads*vdim*dim], out float32 [n, heads*vdim]."""
     require_cuda(z, z_bias, out)
     _require_rows(state)
     n = proj.shape[0]
@@ -624,6 +633,7 @@ def gla(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor,
     _check(core().mlc_gla(_columns(proj, 0), proj.stride(0), q_col, k_col, v_col, z.data_ptr(), _ptr(z_bias), float(tau),
                           state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs, n,
                           heads, dim, vdim, out.data_ptr(), _stream()), "gated linear attention")
+    count_launches(1)
 
 
 # ------------------------------------------------------------------ latent attention (csrc/latent.cu)
@@ -1074,6 +1084,36 @@ def gemm_tcgen05_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
                                         block_rows, n_splits, epilogue, status.data_ptr(), n_sms, _ptr(bias), _ptr(positions),
                                         _ptr(tok_seq), _ptr(rope), rope.shape[0] if rope is not None else 0, q_heads,
                                         kv_heads, head_dim, *cache, _stream()), "tcgen05 matrix product (prompt form)")
+
+
+GROUPED_TILE = 128           # rows per tile of the grouped tcgen05 product: a group's run of rows starts on a multiple of it
+
+
+def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor, epilogue: int = 0,
+                         n_sms: int = 0) -> None:
+    """The prompt form of the tcgen05 product with a matrix per group of rows (csrc/gemm_tcgen05_rows.cu): bfloat16 x
+    [rows, K], rows a multiple of 128; bfloat16 w [groups, n_out, K]; tile_group int32 [rows / 128] gives every tile of
+    128 rows its group (negative: skipped).  EPI_STORE: out [rows, n_out]; EPI_SILU_MUL (w's rows alternate gate and
+    up): out [rows, n_out / 2]."""
+    require_cuda(x, w, tile_group, out)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 matrix product takes bfloat16 operands")
+    if n_sms <= 0:
+        n_sms = _sm_count(x.device)
+    rows, K = x.shape
+    groups, n_out, k2 = w.shape
+    if k2 != K or rows % GROUPED_TILE or tile_group.numel() != rows // GROUPED_TILE or tile_group.dtype != torch.int32:
+        raise KernelError(f"shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, {tile_group.numel()} tiles")
+    if K % 8 or n_out % 16:
+        raise KernelError(f"the grouped tcgen05 product needs an inner size that is a multiple of 8 and a multiple of 16 rows "
+                          f"per group, got {K} and {n_out}")
+    assert out.numel() == rows * (n_out // 2 if epilogue == EPI_SILU_MUL else n_out)
+    # the widest tile that leaves no more than a tile's worth of rounds idle; tiles that hold no rows cost nothing
+    block_rows = gemm_rows_block(rows, n_out, n_sms)
+    status = gemm_status(x.device)
+    _check(core().mlc_gemm_tcgen05_rows_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, n_out, K,
+                                                block_rows, epilogue, status.data_ptr(), n_sms, tile_group.data_ptr(), groups,
+                                                _stream()), "grouped tcgen05 matrix product")
 
 
 @functools.lru_cache(maxsize=None)

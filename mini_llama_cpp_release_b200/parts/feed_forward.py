@@ -117,9 +117,18 @@ class MixtureOfExperts(Part):
         self.router = get(self.name + self.t["router"]).to(torch.float32).contiguous()        # the router is float32 in both modes
         self.router_bias = get(self.name + self.t["router_bias"]).to(torch.float32).contiguous() if self.has_bias else None
         # [E, 2*inter, hidden]: an expert's gate rows, then its up rows; [E, hidden, inter]
-        self.gate_up = torch.stack([torch.cat([get(self._expert(e, "gate")), get(self._expert(e, "up"))], dim=0)
-                                    for e in range(self.E)]).contiguous()
+        gates, ups = [get(self._expert(e, "gate")) for e in range(self.E)], [get(self._expert(e, "up")) for e in range(self.E)]
         self.down = torch.stack([get(self._expert(e, "down")) for e in range(self.E)]).contiguous()
+        # The tensor-core form (bfloat16 engine, sizes the tcgen05 product takes): an expert's gate and up rows alternate,
+        # g0, u0, g1, u1, ..., so that SiLU(gate)·up is the product's epilogue, and runs are padded to its tiles of 128
+        # rows.  Otherwise float32 multiply-adds on [gate; up] with tiles of 64 rows.
+        self.fused = (runtime.dtype == torch.bfloat16 and self.down.dtype == torch.bfloat16 and gates[0].dtype == torch.bfloat16
+                      and self.hidden % 16 == 0 and self.inter % 8 == 0)
+        if self.fused:
+            self.gate_up = torch.stack([torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden)
+                                        for g, u in zip(gates, ups)]).contiguous()
+        else:
+            self.gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]).contiguous()
 
     def weight_bytes(self) -> int:
         """Bytes a step of many tokens reads; a step of few tokens reads `top` experts per token at most."""
@@ -134,29 +143,35 @@ class MixtureOfExperts(Part):
         """(ids int32 [n, top], weights float32 [n, top])."""
         rt = self.runtime
         n = h.shape[0]
-        logits = rt.empty(n, self.E, dtype=torch.float32)
-        kernels.linear_simt(h, self.router, logits)
         ids = rt.empty(n, self.top, dtype=torch.int32)
         weights = rt.empty(n, self.top, dtype=torch.float32)
-        kernels.moe_route(logits, self.router_bias, self.top, ids, weights)
+        kernels.moe_route(h, self.router_bias, self.top, ids, weights, router=self.router)       # logits, choice and weights in one kernel
         return ids, weights
 
     def forward(self, h: torch.Tensor, step=None, residual=None):
         rt = self.runtime
         n = h.shape[0]
         ids, weights = self.route(h)
-        tile = self.TILE
+        tile = kernels.GROUPED_TILE if self.fused else self.TILE
         rows = kernels.moe_plan_rows(n * self.top, self.E, tile)
         row_of = rt.empty(n, self.top, dtype=torch.int32)
         src_tok = rt.empty(rows, dtype=torch.int32)
         tile_expert = rt.empty(rows // tile, dtype=torch.int32)
         kernels.moe_plan(ids, self.E, tile, row_of, src_tok, tile_expert)
+        y = rt.empty(rows, self.hidden, dtype=torch.float32)
+        out = rt.empty(n, self.hidden, dtype=torch.float32)
+        if self.fused:
+            hs = rt.empty(rows, self.hidden)
+            kernels.moe_gather(h, src_tok, hs)                       # the sorted rows, dense, as the product's TMA loads want them
+            act = rt.empty(rows, self.inter)
+            kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
+            kernels.gemm_tcgen05_grouped(act, self.down, tile_expert, y, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
+            kernels.moe_combine(y, row_of, weights, out)
+            return out
         gu = rt.empty(rows, 2 * self.inter)
         kernels.grouped_linear(h, src_tok, self.gate_up, tile_expert, tile, gu)
         act = rt.empty(rows, self.inter)
         kernels.silu_mul(gu, act)
-        y = rt.empty(rows, self.hidden, dtype=torch.float32)
         kernels.grouped_linear(act, None, self.down, tile_expert, tile, y)
-        out = rt.empty(n, self.hidden, dtype=torch.float32)
         kernels.moe_combine(y, row_of, weights, out)
         return out

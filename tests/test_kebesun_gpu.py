@@ -272,6 +272,19 @@ def test_routing_plan_products_and_sum_against_plain_torch(n, E, top):
     val, idx = torch.topk(logits + bias, top, dim=-1)
     assert torch.equal(ids.long(), idx)
     assert torch.allclose(wts, torch.softmax(val, dim=-1), atol=1e-6)
+    # the same with the logits formed inside the kernel from the branch's input and the router's matrix
+    for dtype in (torch.float32, torch.bfloat16):
+        hx = torch.randn(n, 70, generator=g).to(dtype).cuda()
+        router = torch.randn(E, 70, generator=g).cuda()
+        ids2, wts2 = torch.empty_like(ids), torch.empty_like(wts)
+        kernels.moe_route(hx, bias, top, ids2, wts2, router=router)
+        val2, idx2 = torch.topk(hx.double() @ router.double().t() + bias.double(), top, dim=-1)
+        sure = (val2[:, -1] - torch.topk(hx.double() @ router.double().t() + bias.double(), min(E, top + 1), dim=-1).values[:, -1]).abs() > 1e-3
+        sure &= (val2[:, :-1] - val2[:, 1:]).min(dim=-1).values > 1e-3 if top > 1 else True
+        if top == E:
+            sure = torch.ones(n, dtype=torch.bool, device="cuda") & ((val2[:, :-1] - val2[:, 1:]).min(dim=-1).values > 1e-3 if top > 1 else True)
+        assert torch.equal(ids2.long()[sure], idx2[sure])
+        assert torch.allclose(wts2[sure].double(), torch.softmax(val2, dim=-1)[sure], atol=1e-4)
     rows = kernels.moe_plan_rows(n * top, E, tile)
     row_of = torch.empty(n, top, dtype=torch.int32, device="cuda")
     src = torch.empty(rows, dtype=torch.int32, device="cuda")
@@ -309,9 +322,11 @@ def test_gated_linear_attention_kernel_against_a_loop(H, dim, vdim, tau):
     before = state.clone()
     out = torch.empty(n, H * vdim, device="cuda")
     q_col, k_col, v_col = 3, 3 + H * dim, 3 + 2 * H * dim
-    kernels.gla(proj, q_col, k_col, v_col, z, zb, tau, state, step_of(lens, slots), H, dim, vdim, out)
-    p64, z64 = proj.double().cpu(), (z + zb).double().cpu()
+    z64 = (z + zb).double().cpu()
+    kernels.gla(proj, q_col, k_col, v_col, z, zb, tau, state, step_of(lens, slots), H, dim, vdim, out)      # z becomes the decays
+    p64 = proj.double().cpu()
     alpha = torch.exp(torch.nn.functional.logsigmoid(z64) / tau).view(n, H, dim)
+    assert torch.allclose(z.double().cpu().view(n, H, dim), alpha, atol=1e-6)
     q = p64[:, q_col:q_col + H * dim].view(n, H, dim) * dim ** -0.5
     k = p64[:, k_col:k_col + H * dim].view(n, H, dim)
     v = p64[:, v_col:v_col + H * vdim].view(n, H, vdim)
@@ -411,3 +426,37 @@ def test_every_attention_kernel_keeps_the_first_keys_beside_the_window(window, k
     for hd in (64, 128):
         windowed_case("tcgen05", lens, lens, 4, 2, hd, window, keep, seed=8)
         windowed_case("tcgen05", [400, 200], [37, 120], 8, 1, hd, window, keep, seed=9)
+
+
+@pytest.mark.parametrize("n, E, top, K, inter", [(300, 5, 2, 96, 48), (1, 4, 4, 64, 8), (2048, 8, 2, 256, 320), (7, 33, 1, 128, 136)])
+def test_the_grouped_tensor_core_product_against_plain_torch(n, E, top, K, inter):
+    """Rows sorted by expert in runs padded to 128, gate/up with SiLU·mul in the epilogue, then down: against float64."""
+    g = torch.Generator().manual_seed(n + E)
+    tile = kernels.GROUPED_TILE
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(n)]).int().cuda()
+    rows = kernels.moe_plan_rows(n * top, E, tile)
+    row_of = torch.empty(n, top, dtype=torch.int32, device="cuda")
+    src = torch.empty(rows, dtype=torch.int32, device="cuda")
+    tile_e = torch.empty(rows // tile, dtype=torch.int32, device="cuda")
+    kernels.moe_plan(ids, E, tile, row_of, src, tile_e)
+    x = torch.randn(n, K, generator=g).bfloat16().cuda()
+    gate = (torch.randn(E, inter, K, generator=g) * 0.2).bfloat16().cuda()
+    up = (torch.randn(E, inter, K, generator=g) * 0.2).bfloat16().cuda()
+    down = (torch.randn(E, K, inter, generator=g) * 0.2).bfloat16().cuda()
+    gate_up = torch.stack([gate, up], dim=2).reshape(E, 2 * inter, K).contiguous()
+    xs = torch.empty(rows, K, dtype=torch.bfloat16, device="cuda")
+    kernels.moe_gather(x, src, xs)
+    act = torch.empty(rows, inter, dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_tcgen05_grouped(xs, gate_up, tile_e, act, kernels.bindings.EPI_SILU_MUL)
+    y = torch.empty(rows, K, dtype=torch.float32, device="cuda")
+    kernels.gemm_tcgen05_grouped(act, down, tile_e, y, kernels.bindings.EPI_STORE)
+    torch.cuda.synchronize()
+    kernels.check_gemm_status(x.device)
+    r = row_of.long().cpu()
+    for t in range(0, n, max(1, n // 9)):
+        for j in range(top):
+            e = int(ids[t, j])
+            a = pk.silu(gate[e].double() @ x[t].double()) * (up[e].double() @ x[t].double())
+            assert torch.allclose(act[r[t, j]].double(), a, atol=3e-2, rtol=3e-2)
+            want = down[e].double() @ act[r[t, j]].double()
+            assert torch.allclose(y[r[t, j]].double(), want, atol=1e-3, rtol=1e-3)
