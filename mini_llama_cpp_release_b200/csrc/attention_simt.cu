@@ -1,5 +1,6 @@
 // Attention over the paged cache in plain float32 arithmetic (no tensor cores), for any
-// element type of the cache and any head size up to 256.  It is the whole-model 32-bit
+// element type of the cache and any head size up to 512 (a second instance of the kernel, with
+// twice the accumulators, takes the sizes above 256).  It is the whole-model 32-bit
 // path's attention and the yardstick the tensor-core kernels are checked against.
 //
 // One kernel serves prompts, continuation chunks and single decoded tokens: a step gives
@@ -21,8 +22,7 @@ constexpr int ATT_ROWS = 16;       // (token, head) rows per block
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_ROWS_PER_WARP = ATT_ROWS / ATT_WARPS;
 constexpr int ATT_TILE = 32;       // keys per tile: one per lane
-constexpr int ATT_MAX_HD = 256;
-constexpr int ATT_ACC = ATT_MAX_HD / 32;
+constexpr int ATT_MAX_HD = 512;
 
 struct AttnArgs {
     const void* q;            // [N][H][hd]
@@ -43,7 +43,7 @@ struct AttnArgs {
     int n_splits;
 };
 
-template <typename T>
+template <typename T, int ATT_ACC>        // ATT_ACC: output entries a lane holds per row, head size <= 32 * ATT_ACC
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(AttnArgs a, PagedKV c) {
     extern __shared__ float smem[];
@@ -274,23 +274,25 @@ static int launch_attention_simt(const void* q, void* out, int dtype, const int*
     dim3 grid((max_q_len + a.tokens_per_block - 1) / a.tokens_per_block, (unsigned)gy, n_seqs);
     const size_t smem = (size_t)(ATT_ROWS * hd + ATT_TILE * (hd + 1) + ATT_TILE * hd) * sizeof(float);
     cudaError_t e;
+    // one instance per element type and accumulator count; each remembers how much shared memory it was allowed
+#define MLC_SIMT_LAUNCH(T, ACC)                                                                                          \
+    do {                                                                                                                 \
+        static size_t allowed = 48 * 1024;                                                                               \
+        if (smem > allowed) {                                                                                            \
+            e = cudaFuncSetAttribute(attention_simt_kernel<T, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                         \
+            allowed = smem;                                                                                              \
+        }                                                                                                                \
+        attention_simt_kernel<T, ACC><<<grid, ATT_WARPS * 32, smem, s>>>(a, c);                                          \
+    } while (0)
     if (dtype == MLC_DTYPE_F32) {
-        static size_t allowed_f32 = 48 * 1024;
-        if (smem > allowed_f32) {
-            e = cudaFuncSetAttribute(attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            allowed_f32 = smem;
-        }
-        attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, s>>>(a, c);
+        if (hd <= 256) MLC_SIMT_LAUNCH(float, 8);
+        else MLC_SIMT_LAUNCH(float, 16);
     } else {
-        static size_t allowed_bf16 = 48 * 1024;
-        if (smem > allowed_bf16) {
-            e = cudaFuncSetAttribute(attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            allowed_bf16 = smem;
-        }
-        attention_simt_kernel<bf16><<<grid, ATT_WARPS * 32, smem, s>>>(a, c);
+        if (hd <= 256) MLC_SIMT_LAUNCH(bf16, 8);
+        else MLC_SIMT_LAUNCH(bf16, 16);
     }
+#undef MLC_SIMT_LAUNCH
     MLC_LAUNCH_CHECK();
     // With one split the first kernel has written `out` itself and no scratch was touched; with more, every
     // (row, split) pair of the scratch was written above before the merge reads it.

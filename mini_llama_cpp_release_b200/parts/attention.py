@@ -361,8 +361,8 @@ class LatentAttention(GQAttention):
         if self.rot % 2 or self.rot < 0 or self.dim < 0 or self.dim + self.rot <= 0:
             raise ValueError(f"latent attention: a head has {head_dim} plain and {rot_dim} rotated entries; the rotated size must be even")
         self.hd = (self.rank + self.rot + 15) // 16 * 16              # a cached row, and a query row, in the kernels
-        if self.hd > 256:
-            raise ValueError(f"latent attention: kv_rank + rot_dim up to 256 is supported, got {self.rank + self.rot}")
+        if self.hd > 512:
+            raise ValueError(f"latent attention: kv_rank + rot_dim up to 512 is supported, got {self.rank + self.rot}")
         if not scale > 0:
             raise ValueError(f"latent attention: the score's scale must be positive, got {scale}")
         self.scale, self.eps = float(scale), float(norm_eps)
@@ -389,7 +389,9 @@ class LatentAttention(GQAttention):
         self.gain = get(t["dkv_norm"]).to(torch.float32).contiguous()
         self.w_uk, self.w_uv = get(t["uk"]).contiguous(), get(t["uv"]).contiguous()
         self.o = Linear(get(t["o"]), runtime)
-        self.use_tensor_cores = runtime.dtype == torch.bfloat16
+        # rows of more than 256 entries run on the float32-arithmetic kernel in both engine types (the tensor-core
+        # attention kernels are compiled for head sizes up to 256)
+        self.use_tensor_cores = runtime.dtype == torch.bfloat16 and self.hd <= 256
         if self.use_tensor_cores:
             kernels.attention_library(self.hd)
 

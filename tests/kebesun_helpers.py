@@ -93,7 +93,10 @@ LOOPED = model(200, 48, 1e-5, [{"type": "gla", "mlp": dense(40), "mixer": gla(2,
                                {"type": "attention", "mlp": None, "mixer": attention(2, 2, 16, 16, 0.25, {"dims": 16, "base": 1e4})}],
                loop=(0, 2, 4))
 
-CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "attention": ONLY_ATTENTION, "gla": ONLY_GLA, "latent": ONLY_LATENT,
+# a latent of 280 with 24 rotated entries: cached rows of 304, above what the tensor-core attention kernels take
+BIG_LATENT = model(120, 64, 1e-5, [{"type": "latent_attention", "mlp": None, "mixer": latent(2, 24, 24, 16, 280, 0.2, 900.0)}])
+
+CONFIGS = {"big_latent": BIG_LATENT, "mixed": MIXED, "wide": WIDE, "odd": ODD, "attention": ONLY_ATTENTION, "gla": ONLY_GLA, "latent": ONLY_LATENT,
            "moe": ONLY_MOE, "looped": LOOPED}
 
 

@@ -28,7 +28,7 @@ def vocab_of(name):
 # ------------------------------------------------------------------ whole prompts
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name, n", [("attention", 150), ("gla", 70), ("latent", 70), ("moe", 70), ("looped", 70),
+@pytest.mark.parametrize("name, n", [("attention", 150), ("gla", 70), ("latent", 70), ("big_latent", 90), ("moe", 70), ("looped", 70),
                                      ("mixed", 150), ("wide", 200), ("odd", 90)])
 def test_whole_prompt_against_plain(name, n, dtype):
     folder = folder_of(name)
