@@ -7,8 +7,11 @@
 // and everything else that enters the recurrence are float32 whatever the engine's type.
 //
 // Two kernels.  The first turns every decay logit into its decay in place, all tokens and channels at once.  The second
-// walks: a block owns (sequence, head, 16 columns of S); a thread holds two columns x an eighth of the rows (side by
-// side) in registers.  Tokens arrive sixteen at a time through shared memory while the next sixteen are on their way
+// walks: a block owns (sequence, head, 16 columns of S, a slab of its rows); a thread holds two columns x an eighth of
+// the slab's rows (side by side) in registers.  Key channels do not meet until the output's sum over them, so the rows
+// of S can be shared out over blocks: each row slab writes its partial outputs into a slice of its own, and whoever reads
+// the outputs adds the slices up in order.  The host picks the slab so that a step has blocks enough to fill the GPU (a
+// prompt of one sequence: narrow slabs; a decode step of many sequences: the whole head, one slice).  Tokens arrive sixteen at a time through shared memory while the next sixteen are on their way
 // from memory into registers, and are walked four at a time: a row's state takes one multiply-add per token, and the
 // four tokens' output sums, with their three shuffles each, are independent of one another and overlap; their results
 // are stored behind the group.  The small blocks are many (heads x vdim / 16 per sequence), so that a prompt of one
@@ -33,8 +36,10 @@ struct GlaArgs {
     long long state_stride;
     const int* slots;
     const int* cu_seqlens;
-    float* out;                 // [n][H*vdim]
+    float* out;                 // [row slabs][n][H*vdim]
+    long long out_slice;        // floats between the slices of two row slabs
     int H, dim, vdim;
+    int col_slabs;
 };
 
 // z <- sigmoid(z + bias)^(1/tau) = exp(logsigmoid(z + bias) / tau),  logsigmoid(x) = min(x, 0) - log1p(exp(-|x|))
@@ -45,7 +50,22 @@ __global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict_
     z[idx] = expf((fminf(x, 0.0f) - log1pf(expf(-fabsf(x)))) * inv_tau);
 }
 
-template <int ROWS>       // rows of a column one thread holds, side by side: dim <= DP = 8 * ROWS
+// ROWS floats from 8- or 16-byte aligned shared memory
+template <int ROWS>
+__device__ __forceinline__ void load_rows(const float* p, float (&v)[ROWS]) {
+    if (ROWS == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        v[0] = t.x; v[1 % ROWS] = t.y;
+    } else {
+#pragma unroll
+        for (int i4 = 0; i4 < ROWS / 4; ++i4) {
+            const float4 t = reinterpret_cast<const float4*>(p)[i4];
+            v[(4 * i4) % ROWS] = t.x; v[(4 * i4 + 1) % ROWS] = t.y; v[(4 * i4 + 2) % ROWS] = t.z; v[(4 * i4 + 3) % ROWS] = t.w;
+        }
+    }
+}
+
+template <int ROWS>       // rows of a column one thread holds, side by side: a block's slab has DP = 8 * ROWS rows
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_walk_kernel(GlaArgs a) {
     constexpr int DP = 8 * ROWS;
@@ -56,7 +76,8 @@ gla_walk_kernel(GlaArgs a) {
     float* as = ks + GLA_CHUNK * DP;                 // [CHUNK][DP] decays
     float* vs = as + GLA_CHUNK * DP;                 // [CHUNK][COLS]
     const int dim = a.dim, vdim = a.vdim;
-    const int head = blockIdx.x, seq = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
+    const int head = blockIdx.x, seq = blockIdx.y, col0 = (blockIdx.z % a.col_slabs) * GLA_COLS;
+    const int slab = blockIdx.z / a.col_slabs, row0 = slab * DP;           // the block's rows of S: row0 .. row0 + DP - 1
     const int tid = threadIdx.x;
     const int r = tid & 7, cp = tid >> 3;
     const int col = col0 + 2 * cp;
@@ -67,7 +88,7 @@ gla_walk_kernel(GlaArgs a) {
     for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
-            const int row = r * ROWS + i;
+            const int row = row0 + r * ROWS + i;
             S[c][i] = (col + c < vdim && row < dim) ? S_base[(long long)(col + c) * dim + row] : 0.0f;
         }
 
@@ -80,11 +101,11 @@ gla_walk_kernel(GlaArgs a) {
             const int tt = idx / DP, d = idx % DP;
             rq[u] = rk[u] = 0.0f;
             ra[u] = 1.0f;                             // no token, or no such channel: a decay of one, q and k zero
-            if (tt < n_here && d < dim) {
-                const float* row = a.proj + (long long)(c0 + tt) * a.proj_stride + head * dim + d;
+            if (tt < n_here && row0 + d < dim) {
+                const float* row = a.proj + (long long)(c0 + tt) * a.proj_stride + head * dim + row0 + d;
                 rq[u] = row[a.q_col];
                 rk[u] = row[a.k_col];
-                ra[u] = a.decay[(long long)(c0 + tt) * a.H * dim + head * dim + d];
+                ra[u] = a.decay[(long long)(c0 + tt) * a.H * dim + head * dim + row0 + d];
             }
         }
 #pragma unroll
@@ -118,21 +139,17 @@ gla_walk_kernel(GlaArgs a) {
                 if (u >= group) break;
                 const int t = g0 + u;
                 const float2 v2 = *reinterpret_cast<const float2*>(vs + t * GLA_COLS + 2 * cp);
-                const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP + r * ROWS);
-                const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP + r * ROWS);
-                const float4* a4 = reinterpret_cast<const float4*>(as + t * DP + r * ROWS);
+                float qv[ROWS], kv[ROWS], av[ROWS];
+                load_rows<ROWS>(qs + t * DP + r * ROWS, qv);
+                load_rows<ROWS>(ks + t * DP + r * ROWS, kv);
+                load_rows<ROWS>(as + t * DP + r * ROWS, av);
                 float acc0 = 0.0f, acc1 = 0.0f;
 #pragma unroll
-                for (int i4 = 0; i4 < ROWS / 4; ++i4) {
-                    const float4 q = q4[i4], k = k4[i4], al = a4[i4];
-                    const float qv[4] = {q.x, q.y, q.z, q.w}, kv[4] = {k.x, k.y, k.z, k.w}, av[4] = {al.x, al.y, al.z, al.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        S[0][4 * i4 + e] = fmaf(av[e], S[0][4 * i4 + e], kv[e] * v2.x);
-                        S[1][4 * i4 + e] = fmaf(av[e], S[1][4 * i4 + e], kv[e] * v2.y);
-                        acc0 = fmaf(S[0][4 * i4 + e], qv[e], acc0);
-                        acc1 = fmaf(S[1][4 * i4 + e], qv[e], acc1);
-                    }
+                for (int e = 0; e < ROWS; ++e) {
+                    S[0][e] = fmaf(av[e], S[0][e], kv[e] * v2.x);
+                    S[1][e] = fmaf(av[e], S[1][e], kv[e] * v2.y);
+                    acc0 = fmaf(S[0][e], qv[e], acc0);
+                    acc1 = fmaf(S[1][e], qv[e], acc1);
                 }
                 res0[u] = acc0;
                 res1[u] = acc1;
@@ -148,7 +165,7 @@ gla_walk_kernel(GlaArgs a) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     if (u >= group || g0 + u >= n_here) break;
-                    float* o = a.out + (long long)(c0 + g0 + u) * a.H * vdim + head * vdim + col;
+                    float* o = a.out + slab * a.out_slice + (long long)(c0 + g0 + u) * a.H * vdim + head * vdim + col;
                     if (col < vdim) o[0] = res0[u];
                     if (col + 1 < vdim) o[1] = res1[u];
                 }
@@ -159,7 +176,7 @@ gla_walk_kernel(GlaArgs a) {
     for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
-            const int row = r * ROWS + i;
+            const int row = row0 + r * ROWS + i;
             if (col + c < vdim && row < dim) S_base[(long long)(col + c) * dim + row] = S[c][i];
         }
 }
@@ -183,24 +200,39 @@ static int launch_gla(const GlaArgs& a, dim3 grid, cudaStream_t s) {
 
 using namespace mlc;
 
+// Rows of S a thread holds (2, 4, 8, 16 or 32; a block's slab of rows is eight times that) for a step of these sizes: the
+// whole head when the step's blocks fill the GPU anyway, else the widest slab that gives two blocks per SM, down to 16
+// rows.  The outputs come in ceil(dim / (8 * rows)) slices.
+extern "C" int mlc_gla_rows(int n_seqs, int H, int dim, int vdim, int n_sms) {
+    int rows = 4;
+    while (8 * rows < dim && rows < 32) rows *= 2;               // the whole head
+    const long long base = (long long)n_seqs * H * ((vdim + GLA_COLS - 1) / GLA_COLS);
+    while (rows > 2 && base * ((dim + 8 * rows - 1) / (8 * rows)) < 2LL * n_sms) rows /= 2;
+    return rows;
+}
+
 // proj: float32 rows (stride proj_stride) holding q (H x dim) at q_col, k (H x dim) at k_col, v (H x vdim) at v_col.
-// z: float32 [n][H*dim] decay logits (overwritten with the decays), z_bias [H*dim] or null.  state: float32, a slot's row holds H*vdim*dim floats.
-// out: float32 [n][H*vdim].
+// z: float32 [n][H*dim] decay logits (overwritten with the decays), z_bias [H*dim] or null.  state: float32, a slot's row
+// holds H*vdim*dim floats.  rows: what mlc_gla_rows gave.  out: float32 [ceil(dim / (8 * rows))][n][H*vdim], partial
+// outputs to be added up.
 extern "C" int mlc_gla(const float* proj, long long proj_stride, int q_col, int k_col, int v_col, float* z,
                        const float* z_bias, float tau, float* state, long long state_stride, const int* slots,
-                       const int* cu_seqlens, int n_seqs, int n_tokens, int H, int dim, int vdim, float* out, void* stream) {
+                       const int* cu_seqlens, int n_seqs, int n_tokens, int H, int dim, int vdim, int rows, float* out,
+                       void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (H <= 0 || dim <= 0 || dim > 256 || vdim <= 0 || !(tau > 0.0f) || n_seqs > 65535) return MLC_ERR_BAD_SIZE;
+    if (rows != 2 && rows != 4 && rows != 8 && rows != 16 && rows != 32) return MLC_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const long long total = (long long)n_tokens * H * dim;
     gla_decay_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(z, z_bias, total, H * dim, 1.0f / tau);
     MLC_LAUNCH_CHECK();
+    const int col_slabs = (vdim + GLA_COLS - 1) / GLA_COLS, row_slabs = (dim + 8 * rows - 1) / (8 * rows);
     GlaArgs a{proj, proj_stride, q_col, k_col, v_col, z, 1.0f / sqrtf((float)dim), state, state_stride,
-              slots, cu_seqlens, out, H, dim, vdim};
-    const dim3 grid(H, n_seqs, (vdim + GLA_COLS - 1) / GLA_COLS);
-    if (dim <= 32) return launch_gla<4>(a, grid, s);
-    if (dim <= 64) return launch_gla<8>(a, grid, s);
-    if (dim <= 128) return launch_gla<16>(a, grid, s);
+              slots, cu_seqlens, out, (long long)n_tokens * H * vdim, H, dim, vdim, col_slabs};
+    const dim3 grid(H, n_seqs, col_slabs * row_slabs);
+    if (rows == 2) return launch_gla<2>(a, grid, s);
+    if (rows == 4) return launch_gla<4>(a, grid, s);
+    if (rows == 8) return launch_gla<8>(a, grid, s);
+    if (rows == 16) return launch_gla<16>(a, grid, s);
     return launch_gla<32>(a, grid, s);
 }
-

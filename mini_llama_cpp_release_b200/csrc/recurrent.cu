@@ -699,9 +699,11 @@ static cudaError_t launch_delta_rule_group(const DeltaArgs& a, dim3 grid, cudaSt
 }
 
 // ------------------------------------------------------------------ gated RMS norm of each head's output
-// out[t][h][d] = o / sqrt(mean_d(o²) + eps) · w[d] · silu(gate[t][h][d]); a warp per (token, head).
+// out[t][h][d] = o / sqrt(mean_d(o²) + eps) · w[d] · silu(gate[t][h][d]); a warp per (token, head).  o may come as
+// n_slices partial sums [slice][t][h][d], slice_stride floats apart, that are added up in order as they are read.
 template <typename T>
-__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int n_slices, long long slice_stride,
+                                     const float* __restrict__ gate, long long gate_stride,
                                      const float* __restrict__ w, float eps, long long n_rows, int H, int vdim,
                                      T* __restrict__ out) {
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -709,14 +711,19 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
     const int lane = threadIdx.x & 31;
     const long long token = row / H;
     const int head = (int)(row % H);
-    const float* src = o + row * vdim;
+    const float* src0 = o + row * vdim;
+    auto src_at = [&](int d) {
+        float v = src0[d];
+        for (int sl = 1; sl < n_slices; ++sl) v += src0[sl * slice_stride + d];
+        return v;
+    };
     const float* g = gate + token * gate_stride + (long long)head * vdim;
     if (vdim <= 256) {                              // the row, its gates and gains in registers: every load issued at once
         float v[8], z[8], wv[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const int d = lane + 32 * k;
-            v[k] = d < vdim ? src[d] : 0.0f;
+            v[k] = d < vdim ? src_at(d) : 0.0f;
             z[k] = d < vdim ? g[d] : 0.0f;
             wv[k] = d < vdim ? w[d] : 0.0f;
         }
@@ -733,12 +740,15 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
         return;
     }
     float ss = 0.0f;
-    for (int d = lane; d < vdim; d += 32) ss += src[d] * src[d];
+    for (int d = lane; d < vdim; d += 32) {
+        const float v = src_at(d);
+        ss += v * v;
+    }
     ss = warp_sum(ss);
     const float f = 1.0f / sqrtf(ss / (float)vdim + eps);
     for (int d = lane; d < vdim; d += 32) {
         const float z = g[d];
-        out[row * vdim + d] = from_float<T>(src[d] * f * w[d] * (z * sigmoid_f(z)));
+        out[row * vdim + d] = from_float<T>(src_at(d) * f * w[d] * (z * sigmoid_f(z)));
     }
 }
 
@@ -1081,17 +1091,18 @@ extern "C" int mlc_gated_delta_rule(const float* qkv, long long qkv_stride, int 
     return 0;
 }
 
-extern "C" int mlc_gated_rmsnorm(const float* o, const float* gate, long long gate_stride, const float* w, float eps,
+extern "C" int mlc_gated_rmsnorm(const float* o, int n_slices, const float* gate, long long gate_stride, const float* w, float eps,
                                  long long n_tokens, int H, int vdim, void* out, int out_dtype, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || vdim <= 0) return MLC_ERR_BAD_SIZE;
+    if (H <= 0 || vdim <= 0 || n_slices < 1) return MLC_ERR_BAD_SIZE;
+    const long long slice_stride = n_tokens * H * vdim;
     const long long n_rows = n_tokens * H;
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == MLC_DTYPE_F32)
-        gated_rmsnorm_kernel<float><<<blocks, 128, 0, s>>>(o, gate, gate_stride, w, eps, n_rows, H, vdim, (float*)out);
+        gated_rmsnorm_kernel<float><<<blocks, 128, 0, s>>>(o, n_slices, slice_stride, gate, gate_stride, w, eps, n_rows, H, vdim, (float*)out);
     else if (out_dtype == MLC_DTYPE_BF16)
-        gated_rmsnorm_kernel<bf16><<<blocks, 128, 0, s>>>(o, gate, gate_stride, w, eps, n_rows, H, vdim, (bf16*)out);
+        gated_rmsnorm_kernel<bf16><<<blocks, 128, 0, s>>>(o, n_slices, slice_stride, gate, gate_stride, w, eps, n_rows, H, vdim, (bf16*)out);
     else
         return MLC_ERR_BAD_DTYPE;
     MLC_LAUNCH_CHECK();

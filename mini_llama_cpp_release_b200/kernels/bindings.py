@@ -17,7 +17,7 @@ __all__ = [
     "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "PinnedCopy", "decode_advance",
     "layernorm", "qk_norm_rope_cache", "softcap", "convert", "causal_conv", "gated_delta_rule", "gated_rmsnorm", "block_gates",
     "linear_scan", "gates_scan_step", "gates_scan_step_takes",
-    "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "gla", "latent_prepare",
+    "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "gla", "gla_slices", "latent_prepare",
     "head_project", "gemm_tcgen05_grouped", "GROUPED_TILE",
 ]
 
@@ -97,7 +97,7 @@ def core() -> ctypes.CDLL:
             "mlc_softcap": [P, LL, F, P],
             "mlc_causal_conv": [P, LL, P, P, P, I, I, I, P, LL, P, P, P, I, I, I, P, LL, P],
             "mlc_gated_delta_rule": [P, LL, I, I, I, P, LL, I, I, P, P, P, P, LL, P, P, I, I, I, I, I, I, I, P, P],
-            "mlc_gated_rmsnorm": [P, P, LL, P, F, LL, I, I, P, I, P],
+            "mlc_gated_rmsnorm": [P, I, P, LL, P, F, LL, I, I, P, I, P],
             "mlc_block_gates": [P, P, P, P, P, P, I, I, I, F, P, P, P],
             "mlc_linear_scan": [P, P, P, LL, P, P, LL, P, P, I, I, I, F, P, I, P],
             "mlc_gates_scan_step": [P, P, P, P, P, P, F, P, LL, P, P, LL, P, I, I, I, F, P, I, P],
@@ -112,7 +112,7 @@ def core() -> ctypes.CDLL:
             "mlc_moe_gather": [P, I, P, I, I, P, P],
             "mlc_moe_combine": [P, P, P, I, I, I, P, P],
             "mlc_scaled_add": [P, P, I, P, P, I, P, LL, I, P],
-            "mlc_gla": [P, LL, I, I, I, P, P, F, P, LL, P, P, I, I, I, I, I, P, P],
+            "mlc_gla": [P, LL, I, I, I, P, P, F, P, LL, P, P, I, I, I, I, I, I, P, P],
             "mlc_latent_prepare": [P, LL, I, I, P, F, P, P, P, I, I, I, I, I, I, I, P, I, I, P, P, LL, I, I, P],
             "mlc_head_project": [P, I, LL, LL, P, I, LL, LL, LL, P, I, LL, LL, I, I, I, I, P],
             "mlc_linear_simt": [P, I, P, I, P, I, I, I, I, P, LL, I, P],
@@ -133,6 +133,8 @@ def core() -> ctypes.CDLL:
             fn.restype = c_int
         lib.mlc_linear_simt_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         lib.mlc_linear_simt_scratch_floats.restype = c_longlong
+        lib.mlc_gla_rows.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.mlc_gla_rows.restype = c_int
         lib.mlc_set_pdl.argtypes = [c_int]
         lib.mlc_set_pdl.restype = c_int
         lib.mlc_uniform_of.argtypes = [c_ulonglong, c_int, c_int]
@@ -473,11 +475,13 @@ def gated_delta_rule(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gate
 
 def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, gate_col: int, gain: torch.Tensor, eps: float, heads: int,
                   vdim: int, out: torch.Tensor) -> None:
-    """out[t, h, :] = o[t, h, :] / rms · gain · silu(gate[t, gate_col + h*vdim + :]) per head (o float32 [n, heads*vdim])."""
+    """out[t, h, :] = o[t, h, :] / rms · gain · silu(gate[t, gate_col + h*vdim + :]) per head (o float32 [n, heads*vdim], or
+    partial sums [slices, n, heads*vdim] that are added up first)."""
     require_cuda(o, gain, out)
-    n = o.shape[0]
-    assert o.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == vdim and out.shape == o.shape
-    _check(core().mlc_gated_rmsnorm(o.data_ptr(), _columns(gate, gate_col), gate.stride(0), gain.data_ptr(), float(eps), n,
+    n = o.shape[-2]
+    slices = o.shape[0] if o.dim() == 3 else 1
+    assert o.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == vdim and tuple(out.shape) == tuple(o.shape[-2:])
+    _check(core().mlc_gated_rmsnorm(o.data_ptr(), slices, _columns(gate, gate_col), gate.stride(0), gain.data_ptr(), float(eps), n,
                                     heads, vdim, out.data_ptr(), dtype_code(out.dtype), _stream()), "gated head norm")
 
 
@@ -620,19 +624,30 @@ def scaled_add(x: torch.Tensor, y1: torch.Tensor, s1: Optional[torch.Tensor], y2
 
 
 # ------------------------------------------------------------------ gated linear attention (csrc/linear_attention.cu)
+def gla_slices(n_seqs: int, heads: int, dim: int, vdim: int, device: torch.device) -> int:
+    """Slices of partial outputs `gla` writes for a step of these sizes (the rows of the state are shared out over blocks
+    when the step would otherwise leave most of the GPU idle)."""
+    rows = core().mlc_gla_rows(n_seqs, heads, dim, vdim, _sm_count(device))
+    return (dim + 8 * rows - 1) // (8 * rows)
+
+
 def gla(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, z_bias: Optional[torch.Tensor], tau: float,
         state: torch.Tensor, step, heads: int, dim: int, vdim: int, out: torch.Tensor) -> None:
     """S <- diag(sigmoid(z + bias)^(1/tau)) S + k vT, o = ST q dim^-1/2 over the step's tokens; q, k (heads x dim) and v
     (heads x vdim) in the float32 rows `proj`, z float32 [n, heads*dim] (overwritten with the decays), state float32
-    [slots, heads*vdim*dim], out float32 [n, heads*vdim]."""
+    [slots, heads*vdim*dim], out float32 [gla_slices(...), n, heads*vdim]: partial outputs whose sum over the first axis
+    is o."""
     require_cuda(z, z_bias, out)
     _require_rows(state)
     n = proj.shape[0]
-    assert z.dtype == out.dtype == torch.float32 and z.shape == (n, heads * dim) and out.shape == (n, heads * vdim)
+    lib = core()
+    rows = lib.mlc_gla_rows(step.n_seqs, heads, dim, vdim, _sm_count(out.device))
+    slices = (dim + 8 * rows - 1) // (8 * rows)
+    assert z.dtype == out.dtype == torch.float32 and z.shape == (n, heads * dim) and tuple(out.shape) == (slices, n, heads * vdim)
     assert state.shape[1] == heads * dim * vdim
-    _check(core().mlc_gla(_columns(proj, 0), proj.stride(0), q_col, k_col, v_col, z.data_ptr(), _ptr(z_bias), float(tau),
-                          state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs, n,
-                          heads, dim, vdim, out.data_ptr(), _stream()), "gated linear attention")
+    _check(lib.mlc_gla(_columns(proj, 0), proj.stride(0), q_col, k_col, v_col, z.data_ptr(), _ptr(z_bias), float(tau),
+                       state.data_ptr(), state.stride(0), step.slots.data_ptr(), step.cu_seqlens.data_ptr(), step.n_seqs, n,
+                       heads, dim, vdim, rows, out.data_ptr(), _stream()), "gated linear attention")
     count_launches(1)
 
 

@@ -159,11 +159,12 @@ def kebesun(config: KebesunConfig) -> ModelSpec:
         layers.append(LayerSpec(f"l{i}.", PartSpec("block", "parallel", params)))
     n = len(layers)
     order: List[int] = list(range(n))
-    if c.loop is not None and c.loop[1] > c.loop[0]:
+    if c.loop is not None:
         start, stop, times = c.loop
         mix = n                                          # the step before each walk, as one more "layer" without a mixer
         layers.append(LayerSpec("loop.", PartSpec("block", "stream_mix", dict(size=c.hidden_size, tensor="in"))))
-        order = list(range(start)) + ([mix] + list(range(start, stop))) * times + list(range(stop, n))
+        if stop > start:                                 # (an empty run has no walk and no step before one; its tensor is still the file's)
+            order = list(range(start)) + ([mix] + list(range(start, stop))) * times + list(range(stop, n))
     return ModelSpec(
         config=c,
         embedding=PartSpec("embedding", "token_embedding", dict(vocab_size=c.vocab_size, hidden_size=c.hidden_size, tensor="embed")),

@@ -179,7 +179,8 @@ class GatedLinearAttention(Part):
         proj = self.in_proj(h, torch.float32)
         z = rt.empty(n, self.n_qk, dtype=torch.float32)
         kernels.linear_simt(proj[:, self.a_col:self.a_col + self.rank].contiguous(), self.a2, z)
-        o = rt.empty(n, self.n_v, dtype=torch.float32)
+        # partial outputs, one slice per slab of the state's rows; the head norm adds them up as it reads them
+        o = rt.empty(kernels.gla_slices(step.n_seqs, self.H, self.dim, self.vdim, rt.device), n, self.n_v, dtype=torch.float32)
         kernels.gla(proj, 0, self.k_col, self.v_col, z, self.a2_bias, self.tau, memory.state, step, self.H, self.dim, self.vdim, o)
         act = rt.empty(n, self.n_v)
         kernels.gated_rmsnorm(o, proj, self.g_col, self.gain, self.eps, self.H, self.vdim, act)

@@ -39,6 +39,8 @@ def test_the_repeated_run_is_walked_with_a_mixing_step_before_each_walk():
     plain = build_model_spec(ModelConfig.from_dict(kh.ODD))
     assert [e.layer for e in plain.schedule] == [0, 1, 2, 3] and len(plain.layers) == 4
     assert pk.order_of_runs(kh.MIXED) == [[0], [1, 2], [1, 2], [1, 2], [3]]
+    empty = build_model_spec(ModelConfig.from_dict({**kh.ODD, "loop": {"start": 2, "stop": 2, "times": 5}}))
+    assert [e.layer for e in empty.schedule] == [0, 1, 2, 3] and empty.layers[4].block.kind == "stream_mix"    # its tensor is still read
 
 
 def test_what_the_runs_ask_of_the_cache():

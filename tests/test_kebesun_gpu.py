@@ -320,10 +320,12 @@ def test_gated_linear_attention_kernel_against_a_loop(H, dim, vdim, tau):
     zb = (torch.randn(H * dim, generator=g) + 2.0).cuda()
     state = torch.randn(6, H * vdim * dim, generator=g).cuda() * 0.1
     before = state.clone()
-    out = torch.empty(n, H * vdim, device="cuda")
+    parts = torch.empty(kernels.gla_slices(len(lens), H, dim, vdim, proj.device), n, H * vdim, device="cuda")
     q_col, k_col, v_col = 3, 3 + H * dim, 3 + 2 * H * dim
     z64 = (z + zb).double().cpu()
-    kernels.gla(proj, q_col, k_col, v_col, z, zb, tau, state, step_of(lens, slots), H, dim, vdim, out)      # z becomes the decays
+    kernels.gla(proj, q_col, k_col, v_col, z, zb, tau, state, step_of(lens, slots), H, dim, vdim, parts)      # z becomes the decays
+    assert parts.shape[0] > 1 or dim <= 16                    # few blocks: the rows of the state are shared out
+    out = parts.sum(dim=0)
     p64 = proj.double().cpu()
     alpha = torch.exp(torch.nn.functional.logsigmoid(z64) / tau).view(n, H, dim)
     assert torch.allclose(z.double().cpu().view(n, H, dim), alpha, atol=1e-6)
