@@ -909,9 +909,17 @@ def test_tcgen05_attention_refuses_other_head_sizes():
         kernels.attention_tcgen05(q, torch.empty_like(q), z, z[:1], 1, 4, 4, kv, 1.0, 0)
 
 
+def test_the_float32_attention_takes_head_sizes_up_to_512():
+    for dtype in ("float32", "bfloat16"):
+        got, want, _ = attention_case([150, 70, 3], [150, 1, 3], 3, 1, 320, dtype, seed=11)
+        close(got, want, 3e-6 if dtype == "float32" else 1e-2)
+        got, want, _ = attention_case([300], [1], 2, 2, 512, dtype, n_splits=3, seed=12)
+        close(got, want, 3e-6 if dtype == "float32" else 1e-2)
+
+
 def test_refusals_are_errors_not_wrong_results():
-    q = torch.zeros(1, 4 * 320, device=DEV)
-    kv = make_paged([torch.zeros(1, 1, 320)], [torch.zeros(1, 1, 320)], torch.float32)
+    q = torch.zeros(1, 4 * 520, device=DEV)
+    kv = make_paged([torch.zeros(1, 1, 520)], [torch.zeros(1, 1, 520)], torch.float32)
     z = torch.zeros(2, dtype=torch.int32, device=DEV)
     with pytest.raises(kernels.KernelError, match="size"):
         kernels.attention_simt(q, torch.empty_like(q), z, z, 1, 1, 4, kv, 1.0)
