@@ -274,6 +274,35 @@ __global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict
     else x[idx] = v[0];
 }
 
+// x[t][i] += s1[i] · sum_slices y1[.][t][i] + s2[i] · sum_j weights[t][j] · rows[row_of[t][j]][i]: the block's addition with
+// the weighted sum of a token's expert rows made on the way (j in the order of the choices; float32).
+template <int VEC>
+__global__ void scaled_add_experts_kernel(float* __restrict__ x, const float* __restrict__ y1, int slices1, const float* __restrict__ s1,
+                                          const float* __restrict__ rows, const int* __restrict__ row_of,
+                                          const float* __restrict__ weights, int top, const float* __restrict__ s2,
+                                          long long total, int d) {
+    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (idx >= total) return;
+    const long long t = idx / d;
+    const int i = (int)(idx - t * d);
+    float a[VEC], b[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) a[e] = b[e] = 0.0f;
+    for (int s = 0; s < slices1; ++s) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) a[e] += y1[(long long)s * total + idx + e];
+    }
+    for (int j = 0; j < top; ++j) {
+        const float wj = weights[t * top + j];
+        const float* r = rows + (long long)row_of[t * top + j] * d + i;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) b[e] = fmaf(wj, r[e], b[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+        x[idx + e] += (s1 != nullptr ? s1[i + e] * a[e] : a[e]) + (s2 != nullptr ? s2[i + e] * b[e] : b[e]);
+}
+
 }  // namespace mlc
 
 using namespace mlc;
@@ -370,6 +399,22 @@ extern "C" int mlc_scaled_add(float* x, const float* y1, int slices1, const floa
     else
         scaled_add_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, y1, slices1, s1, y2, slices2, s2,
                                                                                                 total, d);
+    MLC_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" int mlc_scaled_add_experts(float* x, const float* y1, int slices1, const float* s1, const float* rows,
+                                      const int* row_of, const float* weights, int top, const float* s2, long long n, int d,
+                                      void* stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || y1 == nullptr || slices1 < 1 || top < 1) return MLC_ERR_BAD_SIZE;
+    const long long total = n * d;
+    if ((d & 3) == 0)
+        scaled_add_experts_kernel<4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            x, y1, slices1, s1, rows, row_of, weights, top, s2, total, d);
+    else
+        scaled_add_experts_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            x, y1, slices1, s1, rows, row_of, weights, top, s2, total, d);
     MLC_LAUNCH_CHECK();
     return 0;
 }

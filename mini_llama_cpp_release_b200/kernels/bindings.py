@@ -17,7 +17,7 @@ __all__ = [
     "launch_count", "reset_launch_count", "library_launch_count", "count_library_launches", "attention_mma_available", "attention_mma", "attention_mma_plan", "attention_decode_cluster_limit", "attention_decode_splits", "attention_decode_clusters_resident", "attention_tcgen05", "attention_tcgen05_takes", "attention_tcgen05_blocks", "attention_library", "gemm_tcgen05", "gemm_qkv_cluster_splits", "gemm_qkv_clusters_resident", "gemm_tcgen05_rows", "gemm_rows_takes", "gemm_rows_add_plan", "gemm_add_plan", "gemm_tcgen05_pair", "gemm_pair_takes", "gemm_prompt", "library_gemm", "gemm_status", "check_gemm_status", "set_pdl", "PinnedCopy", "decode_advance",
     "layernorm", "qk_norm_rope_cache", "softcap", "convert", "causal_conv", "gated_delta_rule", "gated_rmsnorm", "block_gates",
     "linear_scan", "gates_scan_step", "gates_scan_step_takes",
-    "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "gla", "gla_slices", "latent_prepare",
+    "moe_route", "moe_plan", "moe_plan_rows", "grouped_linear", "moe_gather", "moe_combine", "scaled_add", "scaled_add_experts", "gla", "gla_slices", "latent_prepare",
     "head_project", "gemm_tcgen05_grouped", "GROUPED_TILE",
 ]
 
@@ -112,6 +112,7 @@ def core() -> ctypes.CDLL:
             "mlc_moe_gather": [P, I, P, I, I, P, P],
             "mlc_moe_combine": [P, P, P, I, I, I, P, P],
             "mlc_scaled_add": [P, P, I, P, P, I, P, LL, I, P],
+            "mlc_scaled_add_experts": [P, P, I, P, P, P, P, I, P, LL, I, P],
             "mlc_gla": [P, LL, I, I, I, P, P, F, P, LL, P, P, I, I, I, I, I, I, P, P],
             "mlc_latent_prepare": [P, LL, I, I, P, F, P, P, P, I, I, I, I, I, I, I, P, I, I, P, P, LL, I, I, P],
             "mlc_head_project": [P, I, LL, LL, P, I, LL, LL, LL, P, I, LL, LL, I, I, I, I, P],
@@ -621,6 +622,21 @@ def scaled_add(x: torch.Tensor, y1: torch.Tensor, s1: Optional[torch.Tensor], y2
     sl = lambda y: (y.shape[0] if y is not None and y.dim() == 3 else 1)
     _check(core().mlc_scaled_add(x.data_ptr(), y1.data_ptr(), sl(y1), _ptr(s1), _ptr(y2), sl(y2), _ptr(s2), n, d, _stream()),
            "scaled addition")
+
+
+def scaled_add_experts(x: torch.Tensor, y1: torch.Tensor, s1: Optional[torch.Tensor], rows: torch.Tensor, row_of: torch.Tensor,
+                       weights: torch.Tensor, s2: Optional[torch.Tensor]) -> None:
+    """x (float32 [n, d], in place) += s1 · y1 + s2 · f, where f[t] = sum_j weights[t, j] · rows[row_of[t, j]] is the weighted
+    sum of token t's expert rows (`moe_combine`'s result, made on the way instead of stored)."""
+    require_cuda(x, y1, s1, rows, row_of, weights, s2)
+    n, d = x.shape
+    assert y1.dtype == rows.dtype == weights.dtype == torch.float32 and tuple(y1.shape[-2:]) == (n, d) and rows.shape[1] == d
+    assert row_of.dtype == torch.int32 and row_of.shape == weights.shape and row_of.shape[0] == n
+    for f in (s1, s2):
+        assert f is None or (f.dtype == torch.float32 and f.numel() == d)
+    _check(core().mlc_scaled_add_experts(x.data_ptr(), y1.data_ptr(), y1.shape[0] if y1.dim() == 3 else 1, _ptr(s1), rows.data_ptr(),
+                                         row_of.data_ptr(), weights.data_ptr(), row_of.shape[1], _ptr(s2), n, d, _stream()),
+           "scaled addition of expert rows")
 
 
 # ------------------------------------------------------------------ gated linear attention (csrc/linear_attention.cu)

@@ -148,7 +148,13 @@ class ParallelBlock(Part):
                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         h = self.norm.forward(x, pending)
         y = self.mixer.forward(h, step, memory)
-        f = self.feed_forward.forward(h, step) if self.feed_forward is not None else None
+        ff = self.feed_forward
+        if ff is not None and getattr(ff, "defers_sum", False):
+            # a mixture of experts: the weighted sum of a token's expert rows is made by the kernel that adds the branches
+            rows, row_of, weights = ff.forward(h, step, deferred=True)
+            kernels.scaled_add_experts(x, y, self.s1, rows, row_of, weights, self.s2)
+            return x, None
+        f = ff.forward(h, step) if ff is not None else None
         kernels.scaled_add(x, y, self.s1, f, self.s2)
         return x, None
 

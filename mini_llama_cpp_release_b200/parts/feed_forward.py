@@ -148,7 +148,12 @@ class MixtureOfExperts(Part):
         kernels.moe_route(h, self.router_bias, self.top, ids, weights, router=self.router)       # logits, choice and weights in one kernel
         return ids, weights
 
-    def forward(self, h: torch.Tensor, step=None, residual=None):
+    defers_sum = True         # forward(..., deferred=True) may leave the weighted sum of a token's rows to the caller
+
+    def forward(self, h: torch.Tensor, step=None, residual=None, deferred: bool = False):
+        """The mixture's output float32 [n, hidden]; with `deferred`, instead the pieces of its last step, (rows float32
+        [sorted rows, hidden], row_of int32 [n, top], weights float32 [n, top]), for a caller whose own kernel adds
+        sum_j weights[t, j] · rows[row_of[t, j]] into the stream (`kernels.scaled_add_experts`)."""
         rt = self.runtime
         n = h.shape[0]
         ids, weights = self.route(h)
@@ -166,6 +171,8 @@ class MixtureOfExperts(Part):
             act = rt.empty(rows, self.inter)
             kernels.gemm_tcgen05_grouped(hs, self.gate_up, tile_expert, act, kernels.bindings.EPI_SILU_MUL, n_sms=rt.n_sms)
             kernels.gemm_tcgen05_grouped(act, self.down, tile_expert, y, kernels.bindings.EPI_STORE, n_sms=rt.n_sms)
+            if deferred:
+                return y, row_of, weights
             kernels.moe_combine(y, row_of, weights, out)
             return out
         gu = rt.empty(rows, 2 * self.inter)
@@ -173,5 +180,7 @@ class MixtureOfExperts(Part):
         act = rt.empty(rows, self.inter)
         kernels.silu_mul(gu, act)
         kernels.grouped_linear(act, None, self.down, tile_expert, tile, y)
+        if deferred:
+            return y, row_of, weights
         kernels.moe_combine(y, row_of, weights, out)
         return out

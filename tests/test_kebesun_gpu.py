@@ -307,6 +307,13 @@ def test_routing_plan_products_and_sum_against_plain_torch(n, E, top):
     kernels.moe_combine(y, row_of, wts, out)
     want = torch.einsum("tj,tjn->tn", wts, torch.einsum("tjnk,tk->tjn", w[ids.long()], x))
     assert torch.allclose(out, want, atol=1e-4, rtol=1e-4)
+    # the same sum made inside the addition of a block's two branches
+    stream = torch.randn(n, N, generator=g).cuda()
+    branch = torch.randn(2, n, N, generator=g).cuda()
+    s1, s2 = torch.randn(N, generator=g).cuda(), torch.randn(N, generator=g).cuda()
+    expect = stream + s1 * branch.sum(0) + s2 * want
+    kernels.scaled_add_experts(stream, branch, s1, y, row_of, wts, s2)
+    assert torch.allclose(stream, expect, atol=1e-4, rtol=1e-4)
 
 
 @pytest.mark.parametrize("H, dim, vdim, tau", [(3, 24, 40, 8.0), (2, 128, 64, 16.0), (1, 200, 36, 1.0), (5, 8, 8, 2.0), (2, 64, 100, 3.0)])
