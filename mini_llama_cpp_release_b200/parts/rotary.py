@@ -107,7 +107,9 @@ def stretched_frequencies(dims: int, base: float, scaling: Optional[dict]) -> Tu
         f'_i = f_i / factor · ramp_i + f_i · (1 - ramp_i)
 
     so that fast pairs keep their frequency and slow ones are divided by `factor`; cos and sin are both multiplied by
-    0.1 · ln(factor) + 1.  Returns (float32 frequencies [dims/2], that multiplier).  Computed in float64, rounded once."""
+    0.1 · ln(factor) + 1.  With scaling = {factor} alone the stretching is linear: every frequency is divided by the
+    factor (positions count `factor` times slower) and the multiplier is one.  Returns (float32 frequencies [dims/2], that
+    multiplier).  Computed in float64, rounded once."""
     i = np.arange(dims // 2, dtype=np.float64)
     f = np.power(float(base), -2.0 * i / dims)
     if not scaling:

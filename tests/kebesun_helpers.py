@@ -158,7 +158,7 @@ def check(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str, many: bo
     kept = errs[:len(errs) - spared] if spared else errs
     if many:
         mean_tol, max_tol = TOL_MANY[dtype]
-        mean = sum(errs) / len(errs)
-        assert mean <= mean_tol * (1.5 if spared else 1.0) and kept[-1] <= max_tol, f"{what}: mean {mean:.3e}, worst {errs[-1]:.3e}, worst kept {kept[-1]:.3e}"
+        mean = sum(kept) / len(kept)                   # of the rows that are held to the bound: a spared row can be off by its whole size
+        assert mean <= mean_tol and kept[-1] <= max_tol, f"{what}: mean {mean:.3e}, worst {errs[-1]:.3e}, worst kept {kept[-1]:.3e}"
     else:
         assert kept[-1] <= TOL[dtype], f"{what}: worst {errs[-1]:.3e}, worst kept {kept[-1]:.3e}"

@@ -469,3 +469,60 @@ def test_the_grouped_tensor_core_product_against_plain_torch(n, E, top, K, inter
             assert torch.allclose(act[r[t, j]].double(), a, atol=3e-2, rtol=3e-2)
             want = down[e].double() @ act[r[t, j]].double()
             assert torch.allclose(y[r[t, j]].double(), want, atol=1e-3, rtol=1e-3)
+
+
+# ------------------------------------------------------------------ the trace replay program
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_replay_program_runs_batches_that_start_together_and_decode_together(dtype, tmp_path):
+    """`bin/trace_run` as a process: four requests of unequal lengths start in one step, go on one token at a time, the
+    shorter ones end earlier, then a second batch takes the freed slots and pages; every wanted row against the plain
+    implementation."""
+    import json
+    import subprocess
+    import sys
+    import numpy as np
+    name = "mixed"
+    folder = folder_of(name)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    vocab = vocab_of(name)
+    reqs = {f"q{i}": random_tokens(n, vocab, 300 + i) for i, n in enumerate([1 + 6, 45 + 9, 130 + 12, 70 + 12])}
+    heads = {"q0": 1, "q1": 45, "q2": 130, "q3": 70}
+    records, keys, step = [], [], 0
+    for batch in (["q0", "q1", "q2"], ["q3", "q0#2"]):
+        ids = {b: b.split("#")[0] for b in batch}
+        records.append(dict(step=step, entries=[dict(id=b, tokens=reqs[ids[b]][:heads[ids[b]]], want=[0, heads[ids[b]] - 1]) for b in batch], end=[]))
+        keys.append([(ids[b], p) for b in batch for p in (0, heads[ids[b]] - 1)])
+        step += 1
+        live, k = list(batch), 0
+        while live:
+            entries, ks, ends = [], [], []
+            for b in live:
+                toks, pos = reqs[ids[b]], heads[ids[b]] + k
+                entries.append(dict(id=b, tokens=[toks[pos]], want=[0] if pos % 2 == 0 else []))
+                if pos % 2 == 0:
+                    ks.append((ids[b], pos))
+                if pos == len(toks) - 1:
+                    ends.append(b)
+            records.append(dict(step=step, entries=entries, end=ends))
+            keys.append(ks)
+            live = [b for b in live if b not in ends]
+            step += 1
+            k += 1
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", str(out), "--max-tokens", "600"],
+                       input="".join(json.dumps(r) + "\n" for r in records), capture_output=True, text=True, timeout=900, cwd=root)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(records))]
+    ref = {rid: oracle_logits(folder, toks) for rid, toks in reqs.items()}
+    got, want = [], []
+    for i, ks in enumerate(keys):
+        path = out / f"{i}.f32"
+        if not ks:
+            assert not path.exists()
+            continue
+        rows = torch.from_numpy(np.fromfile(str(path), dtype="<f4").reshape(-1, vocab).copy())
+        assert rows.shape[0] == len(ks)
+        got.append(rows)
+        want.append(torch.stack([ref[rid][pos] for rid, pos in ks]))
+    check(torch.cat(got), torch.cat(want), dtype, "replayed batches", many=True)
